@@ -1,0 +1,440 @@
+// bf16 GEMM for sm_100a, with an optional fused reduce-scatter epilogue over peer memory.
+//
+//   C[M,N] = A[M,K] * Bt[N,K]^T      bf16 in, fp32 accumulate in TMEM, bf16 out (RNE)
+//
+// Stands in for micro_tk / kittens_store / dispatch_micro of the reference
+// (distributed-kernels/bf16_gemm/kernel.cpp:89-245, :24-70, :247-251). The reference kernel is a
+// producer/consumer MFMA kernel with a 128x256x64 CTA tile whose epilogue stores each element
+// through iris.store to its own rank. This kernel keeps the contract (same operand layouts, same
+// CTA tile footprint) and nothing of the mechanism:
+//
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of A (128x64) and Bt (256x64) tiles,
+//               128-byte swizzle, into a 4-stage shared-memory ring, completion on mbarriers
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (128x256x16, kind::f16) reading the ring
+//               through shared-memory descriptors, accumulating into one of two 256-column TMEM
+//               buffers; tcgen05.commit frees ring stages and publishes finished accumulators
+//   warps 2-5   epilogue: tcgen05.ld (lane quarter = warp % 4), fp32 -> bf16, then either 16-byte
+//               global stores or swizzled shared-memory staging + TMA bulk stores
+//
+// Persistent: one CTA per SM walks a static tile list in a grouped raster (16 row-tiles per group)
+// so that concurrently running CTAs share A and Bt tiles in L2.
+//
+// Reduce-scatter mode (world > 1): A and Bt hold this rank's K-shard. Each finished 128x256 tile
+// of the partial product is written, as bf16, into slot [rank] of the staging area of the rank
+// that OWNS those rows (peer memory, over NVLink), followed by a release store of the call's
+// epoch into that tile's flag [rank] at the owner. Row-tiles are visited starting with the rows
+// of rank+1 and ending with this rank's own, so every link is busy from the first tile on. After
+// its GEMM tiles, every CTA turns into a reducer for this rank's rows: it waits (bounded) for the
+// `world` flags of a tile, sums the `world` bf16 partials in fp32 in rank order and writes bf16.
+#include "dk_host.h"
+#include "dk_ptx.cuh"
+
+namespace dk {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int EPI_BUF_BYTES = 32 * 128;  // 32 rows x 64 bf16 per epilogue warp
+constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;
+constexpr int CTRL_BYTES = 256;
+constexpr int GEMM_SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + CTRL_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int GROUP_M = 16;
+constexpr int TMEM_COLS = 512;
+
+struct GemmMaps {
+    CUtensorMap a;
+    CUtensorMap b;
+    CUtensorMap out[DK_MAX_RANKS];  // destination seen as [rows_per_rank, N], box 64 x 32
+};
+
+struct GemmArgs {
+    int M, N, K;
+    int tiles_m, tiles_n, num_kb;
+    int world, rank;
+    int rows_per_rank;  // rows of the output owned by one rank (M when world == 1)
+    int m_tile_rot;     // first row-tile visited
+    int epi_mode;       // 0 direct stores, 1 TMA stores
+    int phases;         // bit 0: GEMM tiles, bit 1: reduce this rank's rows
+    __nv_bfloat16* dst[DK_MAX_RANKS];  // per owner: where this rank's partial (or C) goes
+    unsigned* flag_dst[DK_MAX_RANKS];  // per owner: flags [tiles_per_shard][world] at the owner
+    unsigned epoch;
+    const __nv_bfloat16* red_src;  // local staging [world][rows_per_rank][N]
+    __nv_bfloat16* red_out;        // [rows_per_rank][N]
+    const unsigned* red_flags;     // local flags [tiles_per_shard][world]
+    unsigned* status;
+};
+
+enum : unsigned {
+    SITE_EMPTY = 1,
+    SITE_FULL = 2,
+    SITE_TMEM_EMPTY = 3,
+    SITE_TMEM_FULL = 4,
+    SITE_EPI_DONE = 5,
+    SITE_RS_FLAG = 6
+};
+
+__device__ __forceinline__ void tile_coords(int t, const GemmArgs& g, int& m, int& n) {
+    const int per_group = GROUP_M * g.tiles_n;
+    const int grp = t / per_group;
+    const int first_m = grp * GROUP_M;
+    const int gsz = min(g.tiles_m - first_m, GROUP_M);
+    const int r = t - grp * per_group;
+    m = first_m + r % gsz;
+    n = r / gsz;
+    m += g.m_tile_rot;
+    if (m >= g.tiles_m) m -= g.tiles_m;
+}
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    const uint32_t ring = smem_base;
+    const uint32_t epi = smem_base + STAGES * STAGE_BYTES;
+    uint8_t* ctrl = smem + STAGES * STAGE_BYTES + EPI_BYTES;
+    const uint32_t ctrl_u = epi + EPI_BYTES;
+    // control block: 8-byte mbarriers, then the TMEM base address and the abort flag
+    const uint32_t bar_full = ctrl_u;                // STAGES
+    const uint32_t bar_empty = ctrl_u + 8 * STAGES;  // STAGES
+    const uint32_t bar_tfull = ctrl_u + 16 * STAGES;        // 2
+    const uint32_t bar_tempty = ctrl_u + 16 * STAGES + 16;  // 2
+    const uint32_t bar_epi = ctrl_u + 16 * STAGES + 32;     // 1
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(ctrl + 16 * STAGES + 48);
+    volatile int* abort_sm = reinterpret_cast<volatile int*>(ctrl + 16 * STAGES + 56);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const WaitCtx wc{g.status, abort_sm};
+    const int num_tiles = g.tiles_m * g.tiles_n;
+    const bool do_gemm = (g.phases & 1) != 0;
+
+    if (threadIdx.x == 0) {
+        *abort_sm = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(bar_tfull + 8 * a, 1);
+            mbar_init(bar_tempty + 8 * a, 128);
+        }
+        mbar_init(bar_epi, 4);
+        fence_mbar_init();
+        tma_prefetch_desc(&maps.a);
+        tma_prefetch_desc(&maps.b);
+    }
+    if (warp == 1 && do_gemm) {
+        tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+        tmem_relinquish<1>();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = do_gemm ? *tmem_slot : 0u;
+
+    if (do_gemm) {
+        if (warp == 0) {
+            // ------------------------------------------------ TMA producer
+            if (lane == 0) {
+                int s = 0;
+                uint32_t ph = 0;
+                bool ok = true;
+                for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                    int m, n;
+                    tile_coords(t, g, m, n);
+                    for (int kb = 0; kb < g.num_kb; ++kb) {
+                        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, wc, SITE_EMPTY, t)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t full = bar_full + 8 * s;
+                        mbar_expect_tx(full, STAGE_BYTES);
+                        const uint32_t sa = ring + s * STAGE_BYTES;
+                        tma_load_2d(sa, &maps.a, full, kb * BK, m * BM);
+                        tma_load_2d(sa + A_BYTES, &maps.b, full, kb * BK, n * BN);
+                        if (++s == STAGES) {
+                            s = 0;
+                            ph ^= 1;
+                        }
+                    }
+                }
+            }
+        } else if (warp == 1) {
+            // ------------------------------------------------ MMA issuer
+            if (lane == 0) {
+                constexpr uint32_t idesc = umma_idesc(1, 1, BM, BN);
+                int s = 0;
+                uint32_t ph = 0;
+                int acc = 0;
+                uint32_t acc_ph = 0;
+                bool ok = true;
+                for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                    if (!mbar_wait(bar_tempty + 8 * acc, acc_ph ^ 1, wc, SITE_TMEM_EMPTY, t)) break;
+                    tc_fence_after();
+                    const uint32_t d_tmem = tmem_base + acc * BN;
+                    for (int kb = 0; kb < g.num_kb; ++kb) {
+                        if (!mbar_wait(bar_full + 8 * s, ph, wc, SITE_FULL, t)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint32_t sa = ring + s * STAGE_BYTES;
+                        const uint64_t da = umma_desc_sw128(sa);
+                        const uint64_t db = umma_desc_sw128(sa + A_BYTES);
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            // +32 bytes along K inside the 128-byte swizzle row = +2 in the
+                            // descriptor's 16-byte address units
+                            umma_f16<1>(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                        }
+                        umma_commit<1>(bar_empty + 8 * s);
+                        if (++s == STAGES) {
+                            s = 0;
+                            ph ^= 1;
+                        }
+                    }
+                    if (!ok) break;
+                    umma_commit<1>(bar_tfull + 8 * acc);
+                    acc ^= 1;
+                    if (acc == 0) acc_ph ^= 1;
+                }
+            }
+        } else {
+            // ------------------------------------------------ epilogue (warps 2..5)
+            const int q = warp & 3;  // TMEM lane quarter this warp may read
+            const int ew = warp - 2;
+            const uint32_t my_epi = epi + ew * 2 * EPI_BUF_BYTES;
+            int acc = 0;
+            uint32_t acc_ph = 0;
+            uint32_t epi_ph = 0;
+            for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+                int m, n;
+                tile_coords(t, g, m, n);
+                const int owner = (m * BM) / g.rows_per_rank;
+                const int row0 = m * BM - owner * g.rows_per_rank + q * 32;  // row inside dst
+                // the whole warp takes the same branch: tcgen05.ld below is warp-collective
+                if (!__all_sync(0xffffffffu,
+                                mbar_wait(bar_tfull + 8 * acc, acc_ph, wc, SITE_TMEM_FULL, t)))
+                    break;
+                tc_fence_after();
+                const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+                for (int c = 0; c < BN / 64; ++c) {
+                    uint32_t r0[32], r1[32];
+                    tmem_ld_32x32b_x32(t_acc + c * 64, r0);
+                    tmem_ld_32x32b_x32(t_acc + c * 64 + 32, r1);
+                    tmem_ld_wait();
+                    uint32_t p[32];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        p[i] = pack_bf16x2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1]));
+                        p[16 + i] =
+                            pack_bf16x2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1]));
+                    }
+                    const int col0 = n * BN + c * 64;
+                    if (g.epi_mode == 1) {
+                        const uint32_t buf = my_epi + (c & 1) * EPI_BUF_BYTES;
+                        // the store issued two chunks ago has finished reading this buffer
+                        if (lane == 0) tma_store_wait_read<1>();
+                        __syncwarp();
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const uint32_t addr = buf + lane * 128 + ((j ^ (lane & 7)) << 4);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                                         "r"(p[4 * j]), "r"(p[4 * j + 1]), "r"(p[4 * j + 2]),
+                                         "r"(p[4 * j + 3])
+                                         : "memory");
+                        }
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(&maps.out[owner], buf, col0, row0);
+                            tma_store_commit();
+                        }
+                    } else {
+                        const int row = row0 + lane;
+                        const bool row_ok = (m * BM + q * 32 + lane) < g.M;
+                        __nv_bfloat16* dst = g.dst[owner] + static_cast<size_t>(row) * g.N + col0;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            if (row_ok && col0 + 8 * j + 8 <= g.N) {
+                                *reinterpret_cast<uint4*>(dst + 8 * j) =
+                                    make_uint4(p[4 * j], p[4 * j + 1], p[4 * j + 2], p[4 * j + 3]);
+                            }
+                        }
+                    }
+                }
+                // accumulator drained: hand the TMEM buffer back to the MMA warp
+                tc_fence_before();
+                mbar_arrive(bar_tempty + 8 * acc);
+                acc ^= 1;
+                if (acc == 0) acc_ph ^= 1;
+
+                if (g.world > 1) {
+                    // all four warps' stores must have landed before the owner is told
+                    if (g.epi_mode == 1) {
+                        if (lane == 0) tma_store_wait_all<0>();
+                    }
+                    __syncwarp();
+                    if (lane == 0) {
+                        __threadfence_system();
+                        mbar_arrive(bar_epi);
+                    }
+                    if (ew == 0) {
+                        bool landed = true;
+                        if (lane == 0) {
+                            landed = mbar_wait(bar_epi, epi_ph, wc, SITE_EPI_DONE, t);
+                            if (landed) {
+                                const int tile_in_shard =
+                                    ((m * BM - owner * g.rows_per_rank) / BM) * g.tiles_n + n;
+                                __threadfence_system();
+                                signal_store_release_sys(g.flag_dst[owner] +
+                                                             static_cast<size_t>(tile_in_shard) * g.world +
+                                                             g.rank,
+                                                         g.epoch);
+                            }
+                        }
+                        if (!__all_sync(0xffffffffu, landed)) break;
+                    }
+                    epi_ph ^= 1;
+                }
+            }
+            if (g.epi_mode == 1 && lane == 0) tma_store_wait_all<0>();
+        }
+    }
+
+    // ---------------------------------------------------- reduce this rank's rows (world > 1)
+    if ((g.phases & 2) != 0 && g.world > 1) {
+        const int shard_tiles = (g.rows_per_rank / BM) * g.tiles_n;
+        const size_t slot_elems = static_cast<size_t>(g.rows_per_rank) * g.N;
+        for (int rt = blockIdx.x; rt < shard_tiles; rt += gridDim.x) {
+            if (threadIdx.x < g.world) {
+                signal_wait_ge(g.red_flags + static_cast<size_t>(rt) * g.world + threadIdx.x,
+                               g.epoch, wc, SITE_RS_FLAG, rt);
+            }
+            __syncthreads();
+            if (*abort_sm) break;
+            const int tm = rt / g.tiles_n, tn = rt % g.tiles_n;
+            // 128 rows x 256 cols = 4096 16-byte vectors; 32 vectors per row
+            for (int v = threadIdx.x; v < BM * (BN / 8); v += GEMM_THREADS) {
+                const int r = tm * BM + v / (BN / 8);
+                const int cidx = tn * BN + (v % (BN / 8)) * 8;
+                if (cidx + 8 > g.N) continue;
+                const size_t off = static_cast<size_t>(r) * g.N + cidx;
+                float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                for (int s = 0; s < g.world; ++s) {
+                    // L2 read: the partials were written by peers while this kernel ran
+                    const uint4 u = __ldcg(reinterpret_cast<const uint4*>(g.red_src + s * slot_elems + off));
+                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = __bfloat1622float2(h[i]);
+                        acc[2 * i] += f.x;
+                        acc[2 * i + 1] += f.y;
+                    }
+                }
+                uint4 o;
+                o.x = pack_bf16x2(acc[0], acc[1]);
+                o.y = pack_bf16x2(acc[2], acc[3]);
+                o.z = pack_bf16x2(acc[4], acc[5]);
+                o.w = pack_bf16x2(acc[6], acc[7]);
+                *reinterpret_cast<uint4*>(g.red_out + off) = o;
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1 && do_gemm) {
+        __syncwarp();
+        tc_fence_after();
+        if (*abort_sm) {
+            // give copies still in flight time to land before the shared memory goes away
+            const uint64_t t0 = globaltimer_ns();
+            while (globaltimer_ns() - t0 < 200000ull) {
+            }
+        }
+        tmem_dealloc<1>(tmem_base, TMEM_COLS);
+    }
+}
+
+// --------------------------------------------------------------------------------------------
+// host side
+
+static int check_gemm_args(const void* A, const void* Bt, void* C, int M, int N, int K) {
+    DK_REQUIRE(A != nullptr && Bt != nullptr && C != nullptr, "null operand");
+    DK_REQUIRE(M > 0 && N > 0 && K > 0, "M, N, K must be positive");
+    DK_REQUIRE(K % 8 == 0, "K must be a multiple of 8 (16-byte rows for TMA)");
+    DK_REQUIRE(N % 8 == 0, "N must be a multiple of 8 (16-byte output vectors)");
+    return DK_OK;
+}
+
+static int launch_gemm(const GemmMaps& maps, const GemmArgs& args, int grid, cudaStream_t stream) {
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    DK_CUDA_OK(cudaGetDevice(&dev));
+    if (!attr_set[dev & 63]) {
+        DK_CUDA_OK(cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        GEMM_SMEM_BYTES));
+        attr_set[dev & 63] = true;
+    }
+    gemm_bf16_kernel<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(maps, args);
+    DK_CUDA_OK(cudaGetLastError());
+    return DK_OK;
+}
+
+int gemm_bf16_impl(const void* A, const void* Bt, void* C, int M, int N, int K, int epilogue,
+                   cudaStream_t stream) {
+    int rc = check_gemm_args(A, Bt, C, M, N, K);
+    if (rc != DK_OK) return rc;
+    GemmMaps maps;
+    GemmArgs g{};
+    rc = make_tmap_2d(&maps.a, A, 2, K, M, static_cast<uint64_t>(K) * 2, BK, BM);
+    if (rc != DK_OK) return rc;
+    rc = make_tmap_2d(&maps.b, Bt, 2, K, N, static_cast<uint64_t>(K) * 2, BK, BN);
+    if (rc != DK_OK) return rc;
+    rc = make_tmap_2d(&maps.out[0], C, 2, N, M, static_cast<uint64_t>(N) * 2, 64, 32);
+    if (rc != DK_OK) return rc;
+    for (int r = 1; r < DK_MAX_RANKS; ++r) maps.out[r] = maps.out[0];
+    g.M = M;
+    g.N = N;
+    g.K = K;
+    g.tiles_m = (M + BM - 1) / BM;
+    g.tiles_n = (N + BN - 1) / BN;
+    g.num_kb = (K + BK - 1) / BK;
+    g.world = 1;
+    g.rank = 0;
+    g.rows_per_rank = g.tiles_m * BM;  // one owner
+    g.m_tile_rot = 0;
+    g.epi_mode = epilogue < 0 ? 1 : epilogue;
+    g.phases = 1;
+    g.dst[0] = static_cast<__nv_bfloat16*>(C);
+    g.epoch = 0;
+    rc = device_status_ptr(&g.status);
+    if (rc != DK_OK) return rc;
+    int sms = 0;
+    rc = sm_count(&sms);
+    if (rc != DK_OK) return rc;
+    const int tiles = g.tiles_m * g.tiles_n;
+    return launch_gemm(maps, g, tiles < sms ? tiles : sms, stream);
+}
+
+}  // namespace dk
+
+extern "C" int dk_gemm_bf16(const void* A, const void* Bt, void* C, int M, int N, int K,
+                            const dk_view* view, int epilogue, void* stream) {
+    (void)view;  // a plain GEMM writes to local memory only; the view is accepted for symmetry
+    if (epilogue > 1) {
+        dk::set_last_error("argument error: epilogue must be -1, 0 or 1");
+        return DK_ERR_ARG;
+    }
+    return dk::gemm_bf16_impl(A, Bt, C, M, N, K, epilogue, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,117 @@
+/*
+ * dk_b200 -- C ABI of the B200 (sm_100a) multi-GPU hot path.
+ *
+ * One shared library, libdk_b200.so. Plain pointers and sizes only; no C++ or torch types cross
+ * this line. Every function returns 0 (DK_OK) on success or a DK_ERR_* code; dk_strerror() names
+ * it. Buffers are borrowed: the caller keeps them alive until the stream has run the work.
+ * Launches are asynchronous on the given stream (NULL = the legacy default stream, which is what
+ * the reference launches on, distributed-kernels/bf16_gemm/kernel.cpp:82,249-250).
+ *
+ * Reference interfaces these entry points stand in for are cited at each declaration, by path
+ * inside the reference project.
+ */
+#ifndef DK_B200_H
+#define DK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DK_MAX_RANKS 8
+
+enum {
+    DK_OK = 0,
+    DK_ERR_ARG = 1,        /* bad shape, alignment, null pointer, unsupported size */
+    DK_ERR_CUDA = 2,       /* a CUDA runtime/driver call failed; see dk_last_error_string() */
+    DK_ERR_DEVICE = 3,     /* a bounded device-side wait gave up; see dk_last_device_status() */
+    DK_ERR_BOOTSTRAP = 4,  /* rendezvous between ranks failed (socket, timeout, peer gone) */
+    DK_ERR_NOMEM = 5,      /* symmetric heap exhausted */
+    DK_ERR_UNSUPPORTED = 6 /* feature not available on this device/driver */
+};
+
+/*
+ * Device view of the symmetric heap: what a kernel needs to address a peer.
+ * Stands in for iris::iris_device_view (external to the reference tree; used at
+ * distributed-kernels/bf16_gemm/kernel.cpp:25,39,58-59,75 and bound at
+ * distributed-kernels/iris_py.cpp:113-115). base[r] is THIS process's mapping of rank r's heap;
+ * the peer address of a local heap pointer p is base[r] + (p - base[rank]).
+ */
+typedef struct dk_view {
+    int rank;
+    int world;
+    void* base[DK_MAX_RANKS];
+    uint64_t heap_bytes;
+    void* mc_base;   /* NVLS multicast mapping of the heap, NULL when not available */
+    void* heap;      /* host handle (dk_heap*) that owns the collective epoch; NULL if world==1 */
+} dk_view;
+
+const char* dk_strerror(int code);
+/* Text of the last CUDA/bootstrap failure on the calling thread ("" if none). */
+const char* dk_last_error_string(void);
+/* Version of this ABI: major*1000 + minor. */
+int dk_version(void);
+
+/*
+ * Record of the first bounded device-side wait that gave up on the current device since the
+ * last call: out = {code, block, site, detail}; code 0 means none. Clears the record.
+ * The reference has no counterpart (HIP errors are printed and dropped, include/pyutils/util.cuh:10-16).
+ */
+int dk_last_device_status(unsigned out[4]);
+
+/* ------------------------------------------------------------------ symmetric heap */
+/*
+ * Stands in for iris::iris (host runtime; call sites distributed-kernels/iris_py.cpp:55-61,89,
+ * 24,100,105) and iris::mpi::initialize/finalize (iris_py.cpp:55,149-154).
+ *
+ * dk_bootstrap_env: rank/world/local_rank from RANK/WORLD_SIZE/LOCAL_RANK, else
+ * OMPI_COMM_WORLD_RANK/SIZE/LOCAL_RANK, else 0/1/0 (no MPI needed).
+ */
+int dk_bootstrap_env(int* rank, int* world, int* local_rank);
+
+typedef struct dk_heap dk_heap;
+
+/*
+ * Create a heap of `bytes` per rank on the current CUDA device and map every peer's heap
+ * (cuMemCreate + POSIX file-descriptor exchange over a Unix socket + cuMemMap). `rendezvous` names
+ * the Unix socket (NULL: derived from MASTER_PORT / DK_JOB_ID). world == 1 needs no rendezvous.
+ */
+int dk_heap_create(size_t bytes, int rank, int world, const char* rendezvous, dk_heap** out);
+int dk_heap_destroy(dk_heap* h);
+/* Bump allocation with a free list; identical call sequences give identical offsets on every
+ * rank. Returns NULL when exhausted. align must be a power of two (0 = 256). */
+void* dk_heap_alloc(dk_heap* h, size_t bytes, size_t align);
+int dk_heap_free(dk_heap* h, void* p);
+/* Host barrier across ranks (after cudaDeviceSynchronize of the caller's choice). */
+int dk_heap_barrier(dk_heap* h);
+int dk_heap_view(dk_heap* h, dk_view* out);
+/* Bytes still free (largest bump region), for tests. */
+size_t dk_heap_bytes_free(dk_heap* h);
+
+/* Host-only pieces of the bootstrap, callable without a GPU (used by the CPU tests):
+ * rendezvous of `world` processes, exchange of one file descriptor each, barrier. */
+typedef struct dk_comm dk_comm;
+int dk_comm_create(int rank, int world, const char* rendezvous, int timeout_ms, dk_comm** out);
+int dk_comm_destroy(dk_comm* c);
+int dk_comm_barrier(dk_comm* c);
+/* all-gather of one fd per rank: fds_out[world]; fds_out[rank] is a dup of my_fd. */
+int dk_comm_allgather_fd(dk_comm* c, int my_fd, int* fds_out);
+/* all-gather of a fixed-size blob per rank. */
+int dk_comm_allgather(dk_comm* c, const void* mine, size_t bytes, void* all_out);
+
+/* ------------------------------------------------------------------ GEMM */
+/*
+ * C[M,N] = A[M,K] * Bt[N,K]^T, bf16 in, fp32 accumulate (tcgen05/TMEM), bf16 out (round to
+ * nearest even). Row-major, contiguous. K % 8 == 0 and N % 8 == 0.
+ * Replaces dispatch_micro / micro_tk (distributed-kernels/bf16_gemm/kernel.cpp:89-251).
+ * view may be NULL (single GPU). epilogue: 0 = direct vector stores, 1 = TMA bulk stores, -1 = default.
+ */
+int dk_gemm_bf16(const void* A, const void* Bt, void* C, int M, int N, int K,
+                 const dk_view* view, int epilogue, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DK_B200_H */
