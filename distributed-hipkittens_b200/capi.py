@@ -59,9 +59,25 @@ def _declare(L: C.CDLL) -> None:
     L.dk_last_device_status.argtypes = [C.POINTER(C.c_uint * 4)]
     L.dk_bootstrap_env.argtypes = [C.POINTER(i), C.POINTER(i), C.POINTER(i)]
     L.dk_gemm_bf16.argtypes = [vp, vp, vp, i, i, i, C.POINTER(DkView), i, vp]
-    for name in dir(L):
-        pass
-    # optional symbols are declared by the modules that use them (see declare_optional)
+    L.dk_heap_create.argtypes = [sz, i, i, C.c_char_p, C.POINTER(vp)]
+    L.dk_heap_destroy.argtypes = [vp]
+    L.dk_heap_alloc.restype = vp
+    L.dk_heap_alloc.argtypes = [vp, sz, sz]
+    L.dk_heap_free.argtypes = [vp, vp]
+    L.dk_heap_barrier.argtypes = [vp]
+    L.dk_heap_view.argtypes = [vp, C.POINTER(DkView)]
+    L.dk_heap_bytes_free.restype = sz
+    L.dk_heap_bytes_free.argtypes = [vp]
+    L.dk_comm_create.argtypes = [i, i, C.c_char_p, i, C.POINTER(vp)]
+    L.dk_comm_destroy.argtypes = [vp]
+    L.dk_comm_barrier.argtypes = [vp]
+    L.dk_comm_allgather_fd.argtypes = [vp, i, C.POINTER(i)]
+    L.dk_comm_allgather.argtypes = [vp, vp, sz, vp]
+    L.dk_gemm_rs_workspace_bytes.restype = sz
+    L.dk_gemm_rs_workspace_bytes.argtypes = [i, i, i]
+    L.dk_gemm_rs_workspace_init.argtypes = [vp, sz, C.POINTER(DkView), vp]
+    L.dk_gemm_rs.argtypes = [vp, vp, vp, i, i, i, vp, C.POINTER(DkView), vp]
+    L.dk_gemm_rs_phase.argtypes = [vp, vp, vp, i, i, i, vp, C.POINTER(DkView), C.c_uint, i, i, vp]
 
 
 def declare(name: str, argtypes, restype=C.c_int):
@@ -125,3 +141,96 @@ def gemm_bf16(A, Bt, C_out=None, *, epilogue: int = -1, stream=None):
     check(lib().dk_gemm_bf16(_ptr(A), _ptr(Bt), _ptr(C_out), M, N, K, None, epilogue,
                              _stream_ptr(stream)))
     return C_out
+
+
+CTRL_BYTES = 1 << 20  # control block at the start of every rank's heap (signal counters)
+
+
+def make_view(rank: int, world: int, bases, heap_bytes: int, heap=None) -> DkView:
+    v = DkView()
+    v.rank, v.world = rank, world
+    for r in range(world):
+        v.base[r] = bases[r]
+    v.heap_bytes = heap_bytes
+    v.mc_base = None
+    v.heap = heap
+    return v
+
+
+class Heap:
+    """ctypes handle on a symmetric heap (dk_heap_*)."""
+
+    def __init__(self, nbytes: int, rank: int = 0, world: int = 1, rendezvous: str | None = None):
+        self._h = C.c_void_p()
+        rv = rendezvous.encode() if rendezvous else None
+        check(lib().dk_heap_create(nbytes, rank, world, rv, C.byref(self._h)))
+        self.rank, self.world = rank, world
+
+    def alloc(self, nbytes: int, align: int = 256) -> int:
+        p = lib().dk_heap_alloc(self._h, nbytes, align)
+        if not p:
+            raise DkError(ERR_NOMEM, "Failed to allocate iris memory", "")
+        return p
+
+    def free(self, ptr: int) -> None:
+        check(lib().dk_heap_free(self._h, C.c_void_p(ptr)))
+
+    def barrier(self) -> None:
+        check(lib().dk_heap_barrier(self._h))
+
+    def view(self) -> DkView:
+        v = DkView()
+        check(lib().dk_heap_view(self._h, C.byref(v)))
+        return v
+
+    def bytes_free(self) -> int:
+        return lib().dk_heap_bytes_free(self._h)
+
+    def close(self) -> None:
+        if self._h:
+            check(lib().dk_heap_destroy(self._h))
+            self._h = C.c_void_p()
+
+
+def tensor_from_ptr(ptr: int, shape, dtype):
+    """Zero-copy torch view of device memory at `ptr` (the caller keeps the owner alive)."""
+    import torch
+    n = 1
+    for d in shape:
+        n *= d
+    esz = torch.empty((), dtype=dtype).element_size()
+
+    class _W:
+        pass
+    w = _W()
+    w.__cuda_array_interface__ = {"shape": (n * esz,), "typestr": "|u1", "data": (ptr, False),
+                                  "version": 3, "strides": None}
+    return torch.as_tensor(w, device="cuda").view(dtype).reshape(shape)
+
+
+def gemm_rs_workspace_bytes(M: int, N: int, world: int) -> int:
+    return lib().dk_gemm_rs_workspace_bytes(M, N, world)
+
+
+def gemm_rs_workspace_init(ws_ptr: int, nbytes: int, view: DkView, stream=None) -> None:
+    check(lib().dk_gemm_rs_workspace_init(C.c_void_p(ws_ptr), nbytes, C.byref(view), _stream_ptr(stream)))
+
+
+def gemm_rs(A, Bt, out, ws_ptr, view: DkView, stream=None):
+    """out[M/P,N] = reduce-scatter of A[M,K/P] @ Bt[N,K/P]^T over the ranks of `view`."""
+    _need_cuda(A, Bt, out)
+    M, Kloc = A.shape
+    N = Bt.shape[0]
+    check(lib().dk_gemm_rs(_ptr(A), _ptr(Bt), _ptr(out), M, N, Kloc,
+                           C.c_void_p(ws_ptr) if ws_ptr else None, C.byref(view), _stream_ptr(stream)))
+    return out
+
+
+def gemm_rs_phase(A, Bt, out, ws_ptr, view: DkView, seq: int, phases: int, *, epilogue: int = -1,
+                  stream=None):
+    _need_cuda(A, Bt, out)
+    M, Kloc = A.shape
+    N = Bt.shape[0]
+    check(lib().dk_gemm_rs_phase(_ptr(A), _ptr(Bt), _ptr(out), M, N, Kloc, C.c_void_p(ws_ptr),
+                                 C.byref(view), seq, phases, epilogue, _stream_ptr(stream)))
+    return out

@@ -26,6 +26,7 @@
 // of rank+1 and ending with this rank's own, so every link is busy from the first tile on. After
 // its GEMM tiles, every CTA turns into a reducer for this rank's rows: it waits (bounded) for the
 // `world` flags of a tile, sums the `world` bf16 partials in fp32 in rank order and writes bf16.
+#include "dk_heap.h"
 #include "dk_host.h"
 #include "dk_ptx.cuh"
 
@@ -427,7 +428,136 @@ int gemm_bf16_impl(const void* A, const void* Bt, void* C, int M, int N, int K, 
     return launch_gemm(maps, g, tiles < sms ? tiles : sms, stream);
 }
 
+// ---- reduce-scatter ---------------------------------------------------------------------------
+// Workspace layout (identical offset on every rank, inside the symmetric heap):
+//   stage [2 parities][world slots][rows_per_rank][N] bf16, then
+//   flags [2 parities][tiles per shard][world] u32 (offset rounded up to 256 bytes)
+static size_t rs_stage_bytes(int M, int N, int world) {
+    return static_cast<size_t>(2) * world * (M / world) * N * 2;
+}
+static size_t rs_flag_words(int M, int N, int world) {
+    const int shard_tiles = ((M / world) / BM) * ((N + BN - 1) / BN);
+    return static_cast<size_t>(shard_tiles) * world;
+}
+static size_t rs_flags_offset(int M, int N, int world) {
+    return (rs_stage_bytes(M, N, world) + 255) / 256 * 256;
+}
+size_t gemm_rs_workspace_bytes(int M, int N, int world) {
+    if (world <= 1) return 0;
+    return rs_flags_offset(M, N, world) + 2 * rs_flag_words(M, N, world) * 4;
+}
+
+int gemm_rs_impl(const void* A, const void* Bt, void* out, int M, int N, int Kloc, void* workspace,
+                 const dk_view* view, unsigned seq, int phases, int epilogue, cudaStream_t stream) {
+    const int world = view ? view->world : 1;
+    if (world <= 1) {
+        if ((phases & 1) == 0) return DK_OK;
+        return gemm_bf16_impl(A, Bt, out, M, N, Kloc, epilogue, stream);
+    }
+    int rc = check_gemm_args(A, Bt, out, M, N, Kloc);
+    if (rc != DK_OK) return rc;
+    DK_REQUIRE(world <= DK_MAX_RANKS, "world must be <= 8");
+    DK_REQUIRE(view->rank >= 0 && view->rank < world, "rank out of range");
+    DK_REQUIRE(M % (world * BM) == 0, "M must be a multiple of world * 128");
+    DK_REQUIRE(workspace != nullptr, "gemm_rs needs a workspace inside the symmetric heap");
+    DK_REQUIRE(seq != 0, "sequence numbers start at 1");
+    const int rank = view->rank;
+    const int mloc = M / world;
+    const size_t slot_elems = static_cast<size_t>(mloc) * N;
+    const unsigned parity = seq & 1u;
+
+    GemmMaps maps;
+    GemmArgs g{};
+    rc = make_tmap_2d(&maps.a, A, 2, Kloc, M, static_cast<uint64_t>(Kloc) * 2, BK, BM);
+    if (rc != DK_OK) return rc;
+    rc = make_tmap_2d(&maps.b, Bt, 2, Kloc, N, static_cast<uint64_t>(Kloc) * 2, BK, BN);
+    if (rc != DK_OK) return rc;
+    g.M = M;
+    g.N = N;
+    g.K = Kloc;
+    g.tiles_m = M / BM;
+    g.tiles_n = (N + BN - 1) / BN;
+    g.num_kb = (Kloc + BK - 1) / BK;
+    g.world = world;
+    g.rank = rank;
+    g.rows_per_rank = mloc;
+    g.m_tile_rot = ((rank + 1) % world) * (mloc / BM);
+    g.epi_mode = epilogue < 0 ? 1 : epilogue;
+    g.phases = phases;
+    g.epoch = seq;
+    char* ws_local = static_cast<char*>(workspace);
+    const size_t stage_par = static_cast<size_t>(parity) * world * slot_elems * 2;
+    const size_t flags_off = rs_flags_offset(M, N, world) + static_cast<size_t>(parity) * rs_flag_words(M, N, world) * 4;
+    for (int o = 0; o < world; ++o) {
+        char* ws_o = static_cast<char*>(peer_ptr(view, ws_local, o));
+        g.dst[o] = reinterpret_cast<__nv_bfloat16*>(ws_o + stage_par) + static_cast<size_t>(rank) * slot_elems;
+        g.flag_dst[o] = reinterpret_cast<unsigned*>(ws_o + flags_off);
+        rc = make_tmap_2d(&maps.out[o], g.dst[o], 2, N, mloc, static_cast<uint64_t>(N) * 2, 64, 32);
+        if (rc != DK_OK) return rc;
+    }
+    for (int o = world; o < DK_MAX_RANKS; ++o) maps.out[o] = maps.out[0];
+    g.red_src = reinterpret_cast<const __nv_bfloat16*>(ws_local + stage_par);
+    g.red_out = static_cast<__nv_bfloat16*>(out);
+    g.red_flags = reinterpret_cast<const unsigned*>(ws_local + flags_off);
+    rc = device_status_ptr(&g.status);
+    if (rc != DK_OK) return rc;
+    int sms = 0;
+    rc = sm_count(&sms);
+    if (rc != DK_OK) return rc;
+    const int tiles = g.tiles_m * g.tiles_n;
+    return launch_gemm(maps, g, tiles < sms ? tiles : sms, stream);
+}
+
 }  // namespace dk
+
+extern "C" size_t dk_gemm_rs_workspace_bytes(int M, int N, int world) {
+    if (M <= 0 || N <= 0 || world < 1 || world > DK_MAX_RANKS || M % world != 0) return 0;
+    return dk::gemm_rs_workspace_bytes(M, N, world);
+}
+
+extern "C" int dk_gemm_rs_workspace_init(void* workspace, size_t bytes, const dk_view* view,
+                                         void* stream) {
+    if (view == nullptr || view->world <= 1) return DK_OK;
+    DK_REQUIRE(workspace != nullptr && bytes > 0, "null workspace");
+    DK_REQUIRE(dk::in_heap(view, workspace, bytes), "workspace must lie inside the symmetric heap");
+    DK_CUDA_OK(cudaMemsetAsync(workspace, 0, bytes, static_cast<cudaStream_t>(stream)));
+    DK_CUDA_OK(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    dk_heap* h = static_cast<dk_heap*>(view->heap);
+    if (h != nullptr) {
+        {
+            std::lock_guard<std::mutex> lk(h->mu);
+            h->rs_seq[workspace] = 0;
+        }
+        return dk_heap_barrier(h);
+    }
+    return DK_OK;
+}
+
+extern "C" int dk_gemm_rs_phase(const void* A, const void* Bt, void* out, int M, int N, int Kloc,
+                                void* workspace, const dk_view* view, unsigned seq, int phases,
+                                int epilogue, void* stream) {
+    DK_REQUIRE(phases >= 1 && phases <= 3, "phases must be 1 (produce), 2 (reduce) or 3 (both)");
+    DK_REQUIRE(epilogue <= 1, "epilogue must be -1, 0 or 1");
+    return dk::gemm_rs_impl(A, Bt, out, M, N, Kloc, workspace, view, seq, phases, epilogue,
+                            static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dk_gemm_rs(const void* A, const void* Bt, void* out, int M, int N, int Kloc,
+                          void* workspace, const dk_view* view, void* stream) {
+    unsigned seq = 1;
+    if (view != nullptr && view->world > 1) {
+        dk_heap* h = static_cast<dk_heap*>(view->heap);
+        DK_REQUIRE(h != nullptr, "view has no heap handle; use dk_gemm_rs_phase with explicit sequence numbers");
+        DK_REQUIRE(workspace != nullptr && dk::in_heap(view, workspace, dk::gemm_rs_workspace_bytes(M, N, view->world)),
+                   "workspace must lie inside the symmetric heap");
+        std::lock_guard<std::mutex> lk(h->mu);
+        auto it = h->rs_seq.find(workspace);
+        DK_REQUIRE(it != h->rs_seq.end(), "workspace was not initialised with dk_gemm_rs_workspace_init");
+        seq = ++it->second;
+    }
+    return dk::gemm_rs_impl(A, Bt, out, M, N, Kloc, workspace, view, seq, 3, -1,
+                            static_cast<cudaStream_t>(stream));
+}
 
 extern "C" int dk_gemm_bf16(const void* A, const void* Bt, void* C, int M, int N, int K,
                             const dk_view* view, int epilogue, void* stream) {

@@ -226,6 +226,7 @@ int dk_heap_free(dk_heap* h, void* p) {
     }
     size_t start = off, size = it->second;
     h->used_blocks.erase(it);
+    h->rs_seq.erase(p);
     auto next = h->free_blocks.lower_bound(start);
     if (next != h->free_blocks.end() && start + size == next->first) {
         size += next->second;

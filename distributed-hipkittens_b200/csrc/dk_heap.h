@@ -33,6 +33,7 @@ struct dk_heap {
     std::mutex mu;
     std::map<size_t, size_t> free_blocks;  // offset -> size, coalesced
     std::map<size_t, size_t> used_blocks;  // offset -> size
+    std::map<void*, unsigned> rs_seq;      // per GEMM+RS workspace: calls made so far
 };
 
 namespace dk {

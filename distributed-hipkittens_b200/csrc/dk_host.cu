@@ -173,4 +173,23 @@ int dk_last_device_status(unsigned out[4]) {
     return DK_OK;
 }
 
+int dk_device_set(int device) {
+    DK_CUDA_OK(cudaSetDevice(device));
+    return DK_OK;
+}
+int dk_device_get(int* device) {
+    DK_REQUIRE(device != nullptr, "null");
+    DK_CUDA_OK(cudaGetDevice(device));
+    return DK_OK;
+}
+int dk_device_count(int* count) {
+    DK_REQUIRE(count != nullptr, "null");
+    DK_CUDA_OK(cudaGetDeviceCount(count));
+    return DK_OK;
+}
+int dk_device_synchronize(void) {
+    DK_CUDA_OK(cudaDeviceSynchronize());
+    return DK_OK;
+}
+
 }  // extern "C"

@@ -111,6 +111,41 @@ int dk_comm_allgather(dk_comm* c, const void* mine, size_t bytes, void* all_out)
 int dk_gemm_bf16(const void* A, const void* Bt, void* C, int M, int N, int K,
                  const dk_view* view, int epilogue, void* stream);
 
+/*
+ * Row-parallel (K-sharded) GEMM fused with reduce-scatter, no NCCL:
+ *   out[M/P, N] (this rank's rows) = sum over ranks r of A_r[M, K/P] * Bt_r[N, K/P]^T
+ * Every rank calls it with its own K-shard. Partial tiles are pushed as bf16 into the owner's
+ * staging slot over NVLink and summed there in fp32 in rank order. M % (world*128) == 0.
+ * The reference has no reduce-scatter (its kernel stores to its own rank only,
+ * distributed-kernels/bf16_gemm/kernel.cpp:39,58-59; `row_offset` is accepted and unused, :80);
+ * this is the operation BASELINE's configs name, behind the same calling convention.
+ *
+ * `workspace` is dk_gemm_rs_workspace_bytes(M, N, world) bytes allocated from the symmetric heap
+ * at the same offset on every rank and initialised once, collectively, with
+ * dk_gemm_rs_workspace_init (zeroes the flags, synchronises the stream, host barrier).
+ * With world == 1 the call is a plain GEMM and workspace may be NULL.
+ */
+size_t dk_gemm_rs_workspace_bytes(int M, int N, int world);
+int dk_gemm_rs_workspace_init(void* workspace, size_t bytes, const dk_view* view, void* stream);
+int dk_gemm_rs(const void* A, const void* Bt, void* out, int M, int N, int Kloc, void* workspace,
+               const dk_view* view, void* stream);
+/*
+ * The same in explicit phases, for callers that schedule them separately and for running all
+ * ranks of a job on one GPU: phases bit 0 = compute and push partial tiles, bit 1 = wait for the
+ * peers' tiles and reduce this rank's rows. `seq` is the 1-based call number on this workspace
+ * (identical on every rank); the view needs no heap handle here.
+ */
+int dk_gemm_rs_phase(const void* A, const void* Bt, void* out, int M, int N, int Kloc,
+                     void* workspace, const dk_view* view, unsigned seq, int phases, int epilogue,
+                     void* stream);
+
+/* ------------------------------------------------------------------ device helpers */
+/* For hosts that link this library but not the CUDA runtime (the pybind11 modules). */
+int dk_device_set(int device);
+int dk_device_get(int* device);
+int dk_device_count(int* count);
+int dk_device_synchronize(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,159 @@
+"""The drop-in boundary without a GPU: the library loads and exports every declared symbol, the
+pybind11 modules import with the reference's names and error strings, the host bootstrap works
+between processes."""
+import ctypes as C
+import multiprocessing as mp
+import os
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def declared_symbols():
+    names = set()
+    for h in (ROOT / "include").glob("*.h"):
+        names |= set(re.findall(r"\b(dk_[a-z0-9_]+)\s*\(", h.read_text()))
+    return sorted(names)
+
+
+def test_library_exports_every_declared_symbol(capi):
+    L = capi.lib()
+    syms = declared_symbols()
+    assert len(syms) >= 20
+    for s in syms:
+        assert hasattr(L, s), f"{s} is declared in include/ but not exported"
+    assert L.dk_version() >= 1000
+    assert L.dk_strerror(0) == b"ok" and L.dk_strerror(3) == b"device-side wait timed out"
+
+
+def test_bootstrap_env(capi, monkeypatch):
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "OMPI_COMM_WORLD_RANK", "OMPI_COMM_WORLD_SIZE",
+              "OMPI_COMM_WORLD_LOCAL_RANK"):
+        monkeypatch.delenv(k, raising=False)
+    assert capi.bootstrap_env() == (0, 1, 0)
+    monkeypatch.setenv("OMPI_COMM_WORLD_RANK", "3")
+    monkeypatch.setenv("OMPI_COMM_WORLD_SIZE", "4")
+    assert capi.bootstrap_env() == (3, 4, 3)
+    monkeypatch.setenv("RANK", "1")
+    monkeypatch.setenv("WORLD_SIZE", "2")
+    monkeypatch.setenv("LOCAL_RANK", "0")
+    assert capi.bootstrap_env() == (1, 2, 0)
+    monkeypatch.setenv("RANK", "5")
+    with pytest.raises(capi.DkError):
+        capi.bootstrap_env()
+
+
+def test_pybind_surface_matches_reference():
+    import iris_py
+    import tk_kernel
+    for name in ("Iris", "Tensor", "IrisDeviceView", "mpi_init", "mpi_finalize"):
+        assert hasattr(iris_py, name)
+    for m in ("rank", "world_size", "empty", "barrier", "get_device_view"):
+        assert hasattr(iris_py.Iris, m)
+    for m in ("data_ptr", "shape", "dtype", "numel", "nbytes"):
+        assert hasattr(iris_py.Tensor, m)
+    for m in ("cur_rank", "world_size"):
+        assert hasattr(iris_py.IrisDeviceView, m)
+    assert iris_py.mpi_init() == (int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)))
+    assert iris_py.mpi_finalize() is None
+    assert hasattr(tk_kernel, "dispatch_micro") and hasattr(tk_kernel, "gemm_rs")
+
+
+def test_dispatch_micro_argument_errors():
+    """Same checks and messages as the reference's from_object (include/pyutils/pyutils.cuh:14-47)."""
+    import torch
+    import tk_kernel
+    with pytest.raises(RuntimeError, match="Expected a torch.Tensor"):
+        tk_kernel.dispatch_micro(1, 2, 3, None, 1, 1, 1, 0)
+    with pytest.raises(RuntimeError, match="Tensor must be on CUDA device"):
+        tk_kernel.dispatch_micro(torch.zeros(2, 2), torch.zeros(2, 2), torch.zeros(2, 2), None, 2, 2, 2, 0)
+    with pytest.raises(RuntimeError, match="Tensor must be contiguous"):
+        tk_kernel.dispatch_micro(torch.zeros(4, 4).t()[:, :2], 0, 0, None, 2, 2, 2, 0)
+    with pytest.raises(TypeError):
+        tk_kernel.dispatch_micro(torch.zeros(2, 2))  # positional arity is part of the contract
+
+
+def test_product_path_has_no_cpu_fallback(capi):
+    """Without a GPU the operators must fail loudly, not compute on the host."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    a = torch.zeros(128, 64, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        capi.gemm_bf16(a, a)
+    import iris_py
+    with pytest.raises(RuntimeError):
+        iris_py.Iris(16)
+
+
+# ---- host bootstrap between two processes (no GPU involved) -----------------------------------
+def _comm_worker(rank, world, name, q):
+    import sys
+    sys.path.insert(0, str(ROOT))
+    from __graft_entry__ import load_package
+    capi = load_package().capi
+    L = capi.lib()
+    c = C.c_void_p()
+    rc = L.dk_comm_create(rank, world, name.encode(), 20000, C.byref(c))
+    if rc != 0:
+        q.put((rank, "create failed", L.dk_last_error_string().decode()))
+        return
+    # blob all-gather
+    mine = (C.c_int * 2)(rank, 100 + rank)
+    allb = (C.c_int * (2 * world))()
+    rc1 = L.dk_comm_allgather(c, mine, C.sizeof(mine), allb)
+    # fd all-gather: every rank shares a memfd holding its rank
+    fd = os.memfd_create(f"dk{rank}")
+    os.write(fd, bytes([65 + rank]) * 8)
+    fds = (C.c_int * world)()
+    rc2 = L.dk_comm_allgather_fd(c, fd, fds)
+    seen = []
+    for r in range(world):
+        os.lseek(fds[r], 0, os.SEEK_SET)
+        seen.append(os.read(fds[r], 8))
+        os.close(fds[r])
+    rc3 = L.dk_comm_barrier(c)
+    L.dk_comm_destroy(c)
+    q.put((rank, (rc1, rc2, rc3), list(allb), seen))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_comm_rendezvous_fd_exchange_barrier(world):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    name = f"pytest.{os.getpid()}.{world}"
+    ps = [ctx.Process(target=_comm_worker, args=(r, world, name, q)) for r in range(world)]
+    for p in ps:
+        p.start()
+    res = [q.get(timeout=60) for _ in ps]
+    for p in ps:
+        p.join(30)
+    for rank, rcs, blob, seen in res:
+        assert rcs == (0, 0, 0), (rank, rcs, blob)
+        assert blob == [v for r in range(world) for v in (r, 100 + r)]
+        assert seen == [bytes([65 + r]) * 8 for r in range(world)]
+
+
+def _lonely_worker(name, q):
+    import sys
+    sys.path.insert(0, str(ROOT))
+    from __graft_entry__ import load_package
+    L = load_package().capi.lib()
+    c = C.c_void_p()
+    rc = L.dk_comm_create(0, 2, name.encode(), 500, C.byref(c))
+    q.put((rc, L.dk_last_error_string().decode()))
+
+
+def test_comm_missing_rank_times_out_with_an_error():
+    """Failure detection on the host: a rank that never joins ends the rendezvous with an error
+    code after the timeout instead of hanging."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_lonely_worker, args=(f"pytest.lonely.{os.getpid()}", q))
+    p.start()
+    rc, msg = q.get(timeout=30)
+    p.join(10)
+    assert rc == 4 and "timed out" in msg

@@ -1,0 +1,131 @@
+"""The oracle against the golden vectors and against itself (CPU only)."""
+from pathlib import Path
+
+import numpy as np
+import torch
+
+GOLD = Path(__file__).resolve().parent / "golden"
+
+
+def _bf16(a: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16)
+
+
+def test_example_inputs_match_golden(orc):
+    fx = np.load(GOLD / "gemm_example.npz")
+    for rank in (0, 1):
+        A, B = orc.example_inputs(128, 256, 128, rank=rank)
+        assert torch.equal(A, _bf16(fx[f"A{rank}"]))
+        assert torch.equal(B, _bf16(fx["B"]))
+        C_ref = _bf16(fx[f"C{rank}"])
+        # the oracle's fp32 product passes the example's own acceptance test on the golden output
+        ok, err = orc.example_check(orc.gemm_ref(A, B).to(torch.bfloat16), A, B)
+        assert ok and err < 0.02
+        assert orc.rel_fro(C_ref.float(), orc.gemm_ref(A, B)) < 1e-2
+
+
+def test_sharded_equals_unsharded(orc):
+    A, Bt = orc.make_gemm_inputs(256, 128, 512, seed=3)
+    full = orc.gemm_ref(A, Bt)
+    for world in (1, 2, 4, 8):
+        As, Bs = orc.shard_k(A, Bt, world)
+        outs = orc.gemm_rs_ref(As, Bs)
+        got = torch.cat(outs, 0)
+        assert orc.rel_fro(got, full) < 1e-6
+        bf = torch.cat(orc.gemm_rs_bf16_partials_ref(As, Bs), 0)
+        assert orc.rel_fro(bf, full) < 5e-3   # what bf16 partials cost
+
+
+def test_allreduce_ref(orc):
+    xs = orc.make_allreduce_inputs((16, 64), 4)
+    s = orc.allreduce_ref(xs)
+    assert torch.allclose(s, sum(x.double() for x in xs).float(), atol=1e-6)
+
+
+def test_route_permute_golden(orc):
+    fx = np.load(GOLD / "moe_small.npz")
+    logits = torch.from_numpy(fx["logits"])
+    idx, w = orc.moe_route(logits, 2)
+    assert np.array_equal(idx.numpy(), fx["topk_idx"])
+    assert np.allclose(w.numpy(), fx["topk_w"], rtol=1e-6)
+    assert idx[3, 0].item() == 1 or idx[3, 1].item() == 1 or logits[3, 1] < logits[3].topk(2).values[1]
+    rop, por, offs, counts = orc.moe_permute(idx, 8, 128)
+    assert np.array_equal(rop.numpy(), fx["row_of_pair"])
+    assert np.array_equal(por.numpy(), fx["pair_of_row"])
+    assert np.array_equal(offs.numpy(), fx["offsets"])
+    assert np.array_equal(counts.numpy(), fx["counts"])
+
+
+def test_route_tie_break_lower_index(orc):
+    logits = torch.zeros(4, 8)
+    idx, w = orc.moe_route(logits, 3)
+    assert idx.tolist() == [[0, 1, 2]] * 4
+    assert torch.allclose(w, torch.full((4, 3), 1 / 3))
+
+
+def test_permute_properties(orc):
+    g = torch.Generator().manual_seed(0)
+    T, E, k = 300, 16, 4
+    idx, _ = orc.moe_route(torch.randn(T, E, generator=g), k)
+    rop, por, offs, counts = orc.moe_permute(idx, E, 128)
+    assert int(counts.sum()) == T * k
+    assert all(int(o) % 128 == 0 for o in offs)
+    # inverse maps
+    flat = rop.reshape(-1).long()
+    assert torch.equal(por[flat].long(), torch.arange(T * k))
+    assert int((por >= 0).sum()) == T * k
+    # rows of one expert are sorted by (token, slot)
+    for e in range(E):
+        rows = por[int(offs[e]):int(offs[e]) + int(counts[e])].long()
+        assert torch.equal(rows, rows.sort().values)
+        assert (idx.reshape(-1)[rows] == e).all()
+    # empty input
+    rop0, por0, offs0, c0 = orc.moe_permute(torch.zeros(0, k, dtype=torch.int32), E, 128)
+    assert por0.numel() == 0 and int(offs0[-1]) == 0
+
+
+def test_quant_golden_and_roundtrip(orc):
+    fx = np.load(GOLD / "moe_small.npz")
+    x = _bf16(fx["x"])
+    q, s = orc.quant_block128(x)
+    assert np.array_equal(q.numpy(), fx["q"])
+    assert np.array_equal(s.numpy(), fx["s"])
+    assert s[0, 0].item() == 1.0 and int(q[:128, :128].max()) == 0   # all-zero block
+    back = orc.dequant_block128(q, s)
+    assert orc.rel_fro(back, x.float()) < 0.04   # e4m3 has 3 mantissa bits
+    # the block maximum maps to +-448 exactly
+    blk = q[128:, 128:].view(torch.float8_e4m3fn).float().abs().max().item()
+    assert blk == 448.0
+
+
+def test_ffn_and_combine_shapes(orc):
+    T, H, F, E, k = 64, 128, 128, 4, 2
+    x, logits, w13q, w13s, w2q, w2s = orc.make_moe_inputs(T, H, F, E, k, seed=1)
+    idx, w = orc.moe_route(logits, k)
+    rop, por, offs, counts = orc.moe_permute(idx, E)
+    xp = orc.moe_gather_rows(x, por, k)
+    xq, xs = orc.quant_block128(xp)
+    y, hq, hs = orc.moe_ffn_ref(xq, xs, w13q, w13s, w2q, w2s, offs)
+    assert y.shape == (int(offs[-1]), H) and hq.shape == (int(offs[-1]), F)
+    out = orc.moe_combine_ref(y, rop, w)
+    assert out.shape == (T, H) and torch.isfinite(out).all()
+    # padding rows stay zero through the FFN
+    pad = por < 0
+    assert float(y[pad].abs().max()) == 0.0 if pad.any() else True
+
+
+def test_ep_layout_consistent_with_single_rank(orc):
+    g = torch.Generator().manual_seed(2)
+    T, E, k, P = 128, 16, 4, 4
+    idx, _ = orc.moe_route(torch.randn(T, E, generator=g), k)
+    recv_pair, recv_offs, rop, dest = orc.ep_layout(idx, E, P)
+    assert sum(int((rp >= 0).sum()) for rp in recv_pair) == T * k
+    for d in range(P):
+        rp = recv_pair[d]
+        valid = rp[rp >= 0].long()
+        assert (dest.reshape(-1)[valid] == d).all()
+        assert torch.equal(rop.reshape(-1)[valid].long(), (rp >= 0).nonzero().flatten())
+    # with one rank the layout is moe_permute
+    rp1, ro1, rop1, _ = orc.ep_layout(idx, E, 1)
+    rop_s, por_s, offs_s, _ = orc.moe_permute(idx, E)
+    assert torch.equal(rp1[0], por_s) and torch.equal(ro1[0], offs_s) and torch.equal(rop1, rop_s)
