@@ -78,6 +78,9 @@ def _declare(L: C.CDLL) -> None:
     L.dk_gemm_rs_workspace_init.argtypes = [vp, sz, C.POINTER(DkView), vp]
     L.dk_gemm_rs.argtypes = [vp, vp, vp, i, i, i, vp, C.POINTER(DkView), vp]
     L.dk_gemm_rs_phase.argtypes = [vp, vp, vp, i, i, i, vp, C.POINTER(DkView), C.c_uint, i, i, vp]
+    L.dk_allreduce.argtypes = [vp, vp, sz, i, C.POINTER(DkView), vp]
+    L.dk_allreduce_all_ranks.argtypes = [i, C.POINTER(DkView), C.POINTER(vp), C.POINTER(vp), sz, i,
+                                         C.c_uint, vp]
 
 
 def declare(name: str, argtypes, restype=C.c_int):
@@ -234,3 +237,21 @@ def gemm_rs_phase(A, Bt, out, ws_ptr, view: DkView, seq: int, phases: int, *, ep
     check(lib().dk_gemm_rs_phase(_ptr(A), _ptr(Bt), _ptr(out), M, N, Kloc, C.c_void_p(ws_ptr),
                                  C.byref(view), seq, phases, epilogue, _stream_ptr(stream)))
     return out
+
+
+def allreduce(x, out, view: DkView, algo: int = -1, stream=None):
+    """out = sum over ranks of x (bf16, fp32 accumulate). x (and out for two-shot) in the heap."""
+    _need_cuda(x, out)
+    check(lib().dk_allreduce(_ptr(x), _ptr(out), x.numel(), algo, C.byref(view), _stream_ptr(stream)))
+    return out
+
+
+def allreduce_all_ranks(views, xs, outs, algo: int, epoch: int, stream=None):
+    """Every rank of a job in one cooperative launch on this GPU (see dk_allreduce_all_ranks)."""
+    world = len(views)
+    _need_cuda(*xs, *outs)
+    va = (DkView * world)(*views)
+    xa = (C.c_void_p * world)(*[t.data_ptr() for t in xs])
+    oa = (C.c_void_p * world)(*[t.data_ptr() for t in outs])
+    check(lib().dk_allreduce_all_ranks(world, va, xa, oa, xs[0].numel(), algo, epoch, _stream_ptr(stream)))
+    return outs

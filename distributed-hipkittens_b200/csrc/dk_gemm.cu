@@ -23,9 +23,10 @@
 // of the partial product is written, as bf16, into slot [rank] of the staging area of the rank
 // that OWNS those rows (peer memory, over NVLink), followed by a release store of the call's
 // epoch into that tile's flag [rank] at the owner. Row-tiles are visited starting with the rows
-// of rank+1 and ending with this rank's own, so every link is busy from the first tile on. After
-// its GEMM tiles, every CTA turns into a reducer for this rank's rows: it waits (bounded) for the
-// `world` flags of a tile, sums the `world` bf16 partials in fp32 in rank order and writes bf16.
+// of rank+1 and ending with this rank's own, so every link is busy from the first tile on.
+//   warps 6-9   reducers: for every tile of this rank's own rows that this CTA computes, wait
+//               (bounded) for the `world` flags, sum the `world` bf16 partials in fp32 in rank order
+//               and write bf16, while the MMA warp is already working on the next tile.
 #include "dk_heap.h"
 #include "dk_host.h"
 #include "dk_ptx.cuh"
@@ -44,7 +45,8 @@ constexpr int EPI_BUF_BYTES = 32 * 128;  // 32 rows x 64 bf16 per epilogue warp
 constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;
 constexpr int CTRL_BYTES = 256;
 constexpr int GEMM_SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + CTRL_BYTES;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;  // TMA, MMA, 4 epilogue warps, 4 reducer warps
+constexpr int RED_THREADS = 128;
 constexpr int GROUP_M = 16;
 constexpr int TMEM_COLS = 512;
 
@@ -208,7 +210,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                     if (acc == 0) acc_ph ^= 1;
                 }
             }
-        } else {
+        } else if (warp < 6) {
             // ------------------------------------------------ epilogue (warps 2..5)
             const int q = warp & 3;  // TMEM lane quarter this warp may read
             const int ew = warp - 2;
@@ -312,42 +314,66 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
         }
     }
 
-    // ---------------------------------------------------- reduce this rank's rows (world > 1)
-    if ((g.phases & 2) != 0 && g.world > 1) {
-        const int shard_tiles = (g.rows_per_rank / BM) * g.tiles_n;
+    // -------------------------------------------------------- reducers (warps 6..9, world > 1)
+    // They walk the same tile list as the GEMM roles and pick the tiles whose rows this rank owns:
+    // the CTA that computes this rank's own partial of a tile (the last contribution to arrive,
+    // by the visiting order) also sums that tile, while the MMA warp is already on the next one.
+    if (warp >= 6 && (g.phases & 2) != 0 && g.world > 1) {
+        const int rt = threadIdx.x - (GEMM_THREADS - RED_THREADS);
         const size_t slot_elems = static_cast<size_t>(g.rows_per_rank) * g.N;
-        for (int rt = blockIdx.x; rt < shard_tiles; rt += gridDim.x) {
-            if (threadIdx.x < g.world) {
-                signal_wait_ge(g.red_flags + static_cast<size_t>(rt) * g.world + threadIdx.x,
-                               g.epoch, wc, SITE_RS_FLAG, rt);
-            }
-            __syncthreads();
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+            int m, n;
+            tile_coords(t, g, m, n);
+            if ((m * BM) / g.rows_per_rank != g.rank) continue;
+            const int tm = (m * BM - g.rank * g.rows_per_rank) / BM;
+            const int rtile = tm * g.tiles_n + n;
+            if (rt < g.world)
+                signal_wait_ge(g.red_flags + static_cast<size_t>(rtile) * g.world + rt, g.epoch, wc,
+                               SITE_RS_FLAG, rtile);
+            named_bar_sync(2, RED_THREADS);
             if (*abort_sm) break;
-            const int tm = rt / g.tiles_n, tn = rt % g.tiles_n;
-            // 128 rows x 256 cols = 4096 16-byte vectors; 32 vectors per row
-            for (int v = threadIdx.x; v < BM * (BN / 8); v += GEMM_THREADS) {
-                const int r = tm * BM + v / (BN / 8);
-                const int cidx = tn * BN + (v % (BN / 8)) * 8;
-                if (cidx + 8 > g.N) continue;
-                const size_t off = static_cast<size_t>(r) * g.N + cidx;
-                float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                for (int s = 0; s < g.world; ++s) {
-                    // L2 read: the partials were written by peers while this kernel ran
-                    const uint4 u = __ldcg(reinterpret_cast<const uint4*>(g.red_src + s * slot_elems + off));
-                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+            // 128 rows x 32 16-byte vectors; 4 vectors per thread in flight per slot
+#pragma unroll 1
+            for (int i0 = 0; i0 < BM * (BN / 8) / RED_THREADS; i0 += 4) {
+                uint4 v[4][DK_MAX_RANKS];
+                size_t off[4];
+                bool ok[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float2 f = __bfloat1622float2(h[i]);
-                        acc[2 * i] += f.x;
-                        acc[2 * i + 1] += f.y;
-                    }
+                for (int u = 0; u < 4; ++u) {
+                    const int vi = rt + (i0 + u) * RED_THREADS;
+                    const int r = tm * BM + vi / (BN / 8);
+                    const int cidx = n * BN + (vi % (BN / 8)) * 8;
+                    ok[u] = cidx + 8 <= g.N;
+                    off[u] = static_cast<size_t>(r) * g.N + cidx;
+#pragma unroll
+                    for (int s = 0; s < DK_MAX_RANKS; ++s)
+                        if (s < g.world && ok[u])
+                            // L2 read: the partials were written by peers while this kernel ran
+                            v[u][s] = __ldcg(reinterpret_cast<const uint4*>(g.red_src + s * slot_elems + off[u]));
                 }
-                uint4 o;
-                o.x = pack_bf16x2(acc[0], acc[1]);
-                o.y = pack_bf16x2(acc[2], acc[3]);
-                o.z = pack_bf16x2(acc[4], acc[5]);
-                o.w = pack_bf16x2(acc[6], acc[7]);
-                *reinterpret_cast<uint4*>(g.red_out + off) = o;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (!ok[u]) continue;
+                    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+                    for (int s = 0; s < DK_MAX_RANKS; ++s) {
+                        if (s < g.world) {
+                            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[u][s]);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float2 f = __bfloat1622float2(h[i]);
+                                acc[2 * i] += f.x;
+                                acc[2 * i + 1] += f.y;
+                            }
+                        }
+                    }
+                    uint4 o;
+                    o.x = pack_bf16x2(acc[0], acc[1]);
+                    o.y = pack_bf16x2(acc[2], acc[3]);
+                    o.z = pack_bf16x2(acc[4], acc[5]);
+                    o.w = pack_bf16x2(acc[6], acc[7]);
+                    *reinterpret_cast<uint4*>(g.red_out + off[u]) = o;
+                }
             }
         }
     }

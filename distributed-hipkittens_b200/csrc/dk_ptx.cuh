@@ -86,7 +86,7 @@ struct WaitCtx {
 
 enum : unsigned { DK_DEV_OK = 0, DK_DEV_TIMEOUT = 1, DK_DEV_PEER_TIMEOUT = 2 };
 
-__device__ __noinline__ void record_timeout(const WaitCtx& w, unsigned code, unsigned site,
+static __device__ __noinline__ void record_timeout(const WaitCtx& w, unsigned code, unsigned site,
                                             unsigned detail) {
     *w.abort_sm = 1;
     if (w.status != nullptr && atomicCAS(w.status, 0u, code) == 0u) {

@@ -128,6 +128,14 @@ void gemm_rs(py::object A, py::object Bt, py::object Out, py::object view) {
     throw_on(dk_gemm_rs(a.ptr, b.ptr, o.ptr, M, N, Kloc, ws, v, stream), "gemm_rs");
 }
 
+void allreduce(py::object X, py::object Out, py::object view, int algo) {
+    TensorArg x = tensor_arg(X, "torch.bfloat16");
+    TensorArg o = tensor_arg(Out, "torch.bfloat16");
+    if (x.numel() != o.numel()) throw std::runtime_error("X and Out must hold the same number of elements");
+    throw_on(dk_allreduce(x.ptr, o.ptr, static_cast<size_t>(x.numel()), algo, view_arg(view), current_stream()),
+             "allreduce");
+}
+
 py::tuple device_status() {
     unsigned st[4] = {0, 0, 0, 0};
     throw_on(dk_last_device_status(st), "device_status");
@@ -143,6 +151,8 @@ PYBIND11_MODULE(tk_kernel, m) {
           "A, B, C, iris_view, M_local, N, K, row_offset");
     m.def("gemm_rs", &gemm_rs,
           "Out[M/P,N] = reduce-scatter over ranks of A[M,K/P] @ Bt[N,K/P]^T. Positional: A, Bt, Out, view");
+    m.def("allreduce", &allreduce, py::arg("X"), py::arg("Out"), py::arg("view"), py::arg("algo") = -1,
+          "Out = sum over ranks of X (bf16). algo: -1 auto, 0 one-shot, 1 two-shot, 2 NVLS");
     m.def("device_status", &device_status,
           "(code, block, site, detail) of the first device-side wait that gave up; clears it");
 }

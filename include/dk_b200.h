@@ -139,6 +139,25 @@ int dk_gemm_rs_phase(const void* A, const void* Bt, void* out, int M, int N, int
                      void* workspace, const dk_view* view, unsigned seq, int phases, int epilogue,
                      void* stream);
 
+/* ------------------------------------------------------------------ all-reduce */
+/*
+ * out = sum over ranks of x, n bf16 elements (n % 8 == 0), fp32 accumulation in rank order, so
+ * every rank ends with bit-identical results. x must lie inside the symmetric heap at the same
+ * offset on every rank. algo: -1 auto by message size (DK_ALLREDUCE_ONESHOT_MAX_BYTES overrides
+ * the crossover), 0 one-shot (every rank reads all inputs; out may be any local buffer, not x),
+ * 1 two-shot (reduce a slice, push it to every rank; out must lie inside the heap, may alias x;
+ * n % (8*world) == 0), 2 NVLS (DK_ERR_UNSUPPORTED: this build maps no multicast object).
+ * world == 1 copies x to out. The reference has no counterpart: it contains no collective.
+ */
+int dk_allreduce(const void* x, void* out, size_t n, int algo, const dk_view* view, void* stream);
+/*
+ * All ranks of a job inside ONE cooperative launch on one GPU (blockIdx.y = rank): views[q],
+ * x[q], out[q] describe rank q, whose "heap" is a region of this GPU's memory. `epoch` is the
+ * 1-based call number shared by all ranks. For single-GPU testing of the multi-rank protocol.
+ */
+int dk_allreduce_all_ranks(int world, const dk_view* views, const void* const* x, void* const* out,
+                           size_t n, int algo, unsigned epoch, void* stream);
+
 /* ------------------------------------------------------------------ device helpers */
 /* For hosts that link this library but not the CUDA runtime (the pybind11 modules). */
 int dk_device_set(int device);
