@@ -79,6 +79,14 @@ def _declare(L: C.CDLL) -> None:
     L.dk_gemm_rs.argtypes = [vp, vp, vp, i, i, i, vp, C.POINTER(DkView), vp]
     L.dk_gemm_rs_phase.argtypes = [vp, vp, vp, i, i, i, vp, C.POINTER(DkView), C.c_uint, i, i, vp]
     L.dk_allreduce.argtypes = [vp, vp, sz, i, C.POINTER(DkView), vp]
+    L.dk_moe_route.argtypes = [vp, i, i, i, vp, vp, vp]
+    L.dk_moe_permute_scratch_bytes.restype = sz
+    L.dk_moe_permute_scratch_bytes.argtypes = [i, i, i]
+    L.dk_moe_rows_capacity.restype = sz
+    L.dk_moe_rows_capacity.argtypes = [i, i, i, i]
+    L.dk_moe_permute.argtypes = [vp, i, i, i, i, i, vp, vp, i, vp, vp, vp, sz, vp]
+    L.dk_quant_block128.argtypes = [vp, i, i, vp, i, i, vp, vp, vp]
+    L.dk_moe_combine.argtypes = [vp, vp, vp, i, i, i, vp, vp]
     L.dk_allreduce_all_ranks.argtypes = [i, C.POINTER(DkView), C.POINTER(vp), C.POINTER(vp), sz, i,
                                          C.c_uint, vp]
 
@@ -255,3 +263,66 @@ def allreduce_all_ranks(views, xs, outs, algo: int, epoch: int, stream=None):
     oa = (C.c_void_p * world)(*[t.data_ptr() for t in outs])
     check(lib().dk_allreduce_all_ranks(world, va, xa, oa, xs[0].numel(), algo, epoch, _stream_ptr(stream)))
     return outs
+
+
+# ---------------------------------------------------------------------------- MoE
+def moe_route(logits, k: int, stream=None):
+    """(topk_idx int32 [T,k], topk_w fp32 [T,k]) from fp32 logits [T,E]."""
+    import torch
+    _need_cuda(logits)
+    if logits.dtype != torch.float32:
+        raise RuntimeError("moe_route expects float32 logits")
+    T, E = logits.shape
+    idx = torch.empty((T, k), dtype=torch.int32, device=logits.device)
+    w = torch.empty((T, k), dtype=torch.float32, device=logits.device)
+    check(lib().dk_moe_route(_ptr(logits), T, E, k, _ptr(idx), _ptr(w), _stream_ptr(stream)))
+    return idx, w
+
+
+def moe_permute(topk_idx, E: int, pad: int = 128, experts_per_segment: int | None = None, stream=None):
+    """Returns (row_of_pair [T,k], pair_of_row [nseg, cap], offsets [nseg, seg+1], counts [E]),
+    all int32 on the device. With one segment the first two dimensions are squeezed."""
+    import torch
+    _need_cuda(topk_idx)
+    T, k = topk_idx.shape
+    seg = E if experts_per_segment is None else experts_per_segment
+    nseg = E // seg
+    cap = lib().dk_moe_rows_capacity(T, k, seg, pad)
+    dev = topk_idx.device
+    rop = torch.empty((T, k), dtype=torch.int32, device=dev)
+    por = torch.empty((nseg, cap), dtype=torch.int32, device=dev)
+    offs = torch.empty((nseg, seg + 1), dtype=torch.int32, device=dev)
+    counts = torch.empty((E,), dtype=torch.int32, device=dev)
+    sb = lib().dk_moe_permute_scratch_bytes(T, k, E)
+    scratch = torch.empty((sb,), dtype=torch.uint8, device=dev)
+    check(lib().dk_moe_permute(_ptr(topk_idx), T, k, E, pad, seg, _ptr(rop), _ptr(por), cap, _ptr(offs),
+                               _ptr(counts), _ptr(scratch), sb, _stream_ptr(stream)))
+    if nseg == 1:
+        return rop, por[0], offs[0], counts
+    return rop, por, offs, counts
+
+
+def quant_block128(x, rows: int | None = None, row_map=None, map_mode: int = 0, k: int = 1, stream=None):
+    """(q uint8 [R,C], s fp32 [R/128,C/128]) from bf16 x; see dk_quant_block128 for the row map."""
+    import torch
+    _need_cuda(x)
+    if x.dtype != torch.bfloat16:
+        raise RuntimeError("quant_block128 expects bfloat16")
+    R = x.shape[0] if rows is None else rows
+    Cc = x.shape[1]
+    q = torch.empty((R, Cc), dtype=torch.uint8, device=x.device)
+    s = torch.empty((R // 128, Cc // 128), dtype=torch.float32, device=x.device)
+    check(lib().dk_quant_block128(_ptr(x), R, Cc, _ptr(row_map) if row_map is not None else None,
+                                  map_mode, k, _ptr(q), _ptr(s), _stream_ptr(stream)))
+    return q, s
+
+
+def moe_combine(y, row_of_pair, topk_w, stream=None):
+    import torch
+    _need_cuda(y, row_of_pair, topk_w)
+    T, k = row_of_pair.shape
+    H = y.shape[1]
+    out = torch.empty((T, H), dtype=torch.bfloat16, device=y.device)
+    check(lib().dk_moe_combine(_ptr(y), _ptr(row_of_pair), _ptr(topk_w), T, k, H, _ptr(out),
+                               _stream_ptr(stream)))
+    return out

@@ -1,0 +1,395 @@
+// MoE routing, permutation, 128x128 block quantisation to e4m3, and combine: the HBM-bound
+// integer/byte kernels around the fp8 grouped GEMM.
+//
+// The reference has no MoE code. The nearest patterns it holds are the block-scaled fp8 fixtures
+// (tests/unit/cdna4/warp/register/tile/mma_scaled.cu:200-258: quantise, CPU truth dequantises per
+// block), whose scale format (1x32 e8m0) differs from the 128x128 fp32 blocks used here.
+//
+// Everything index-like is deterministic and order-preserving (scans, no atomics whose order
+// could leak into the result), so it is bit-exact against the CPU definition:
+//   route     top-k on the raw fp32 logits, ties to the lower expert index, output in descending
+//             logit order; weights = softmax over all experts gathered and renormalised
+//   permute   pairs (token, slot) grouped by expert, each expert padded to `pad` rows; inside an
+//             expert, pairs keep their (token, slot) order
+//   quant     per 128x128 block s = amax/448 (1 when the block is all zero), q = RNE(x / s)
+//   combine   out[t] = sum_j w[t,j] * Y[row(t,j)] in fp32, slot order
+#include <cuda_fp8.h>
+
+#include "dk_heap.h"
+#include "dk_host.h"
+#include "dk_ptx.cuh"
+
+namespace dk {
+
+// ------------------------------------------------------------------------------------ route
+constexpr int ROUTE_MAX_E = 256;
+constexpr int ROUTE_MAX_K = 8;
+
+// One warp per token. Lane l holds experts l, l+32, ... (E <= 256 -> at most 8 per lane).
+__global__ void __launch_bounds__(256) moe_route_kernel(const float* __restrict__ logits, int T, int E,
+                                                        int k, int* __restrict__ topk_idx,
+                                                        float* __restrict__ topk_w) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= T) return;
+    const float* row = logits + static_cast<size_t>(warp) * E;
+    float v[ROUTE_MAX_E / 32];
+    bool taken[ROUTE_MAX_E / 32];
+#pragma unroll
+    for (int i = 0; i < ROUTE_MAX_E / 32; ++i) {
+        const int e = lane + 32 * i;
+        v[i] = e < E ? row[e] : -INFINITY;
+        taken[i] = e >= E;
+    }
+    float sel_v[ROUTE_MAX_K];
+    int sel_e[ROUTE_MAX_K];
+#pragma unroll 1
+    for (int j = 0; j < k; ++j) {
+        // best of this lane: largest value, lowest index among equals (ascending scan, strict >)
+        float bv = -INFINITY;
+        int be = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < ROUTE_MAX_E / 32; ++i) {
+            const int e = lane + 32 * i;
+            if (!taken[i] && (be == 0x7fffffff || v[i] > bv)) {
+                bv = v[i];
+                be = e;
+            }
+        }
+        // warp arg-max with the same tie rule
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+            const bool other_valid = oe != 0x7fffffff;
+            const bool mine_valid = be != 0x7fffffff;
+            if (other_valid && (!mine_valid || ov > bv || (ov == bv && oe < be))) {
+                bv = ov;
+                be = oe;
+            }
+        }
+        sel_v[j] = bv;
+        sel_e[j] = be;
+        if ((be & 31) == lane) {
+#pragma unroll
+            for (int i = 0; i < ROUTE_MAX_E / 32; ++i)
+                if (lane + 32 * i == be) taken[i] = true;
+        }
+    }
+    if (lane == 0) {
+        // renormalised softmax over the selection: the full-softmax denominator cancels
+        const float m = sel_v[0];
+        float p[ROUTE_MAX_K];
+        float sum = 0.f;
+        for (int j = 0; j < k; ++j) {
+            p[j] = expf(sel_v[j] - m);
+            sum += p[j];
+        }
+        for (int j = 0; j < k; ++j) {
+            topk_idx[static_cast<size_t>(warp) * k + j] = sel_e[j];
+            topk_w[static_cast<size_t>(warp) * k + j] = p[j] / sum;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------ permute
+// Stable counting sort of the pairs by expert in three launches:
+//   A  per-chunk histograms                 -> scratch[chunk][E]
+//   B  (one block) per-expert scan over chunks, padded offsets (restarting every `seg` experts)
+//   C  position of every pair = offset[e] + pairs of e in earlier chunks + earlier pairs of e in
+//      this chunk (warp match + per-warp counts)
+constexpr int PERM_CHUNK = 1024;  // pairs per block, one per thread
+
+__global__ void __launch_bounds__(PERM_CHUNK) moe_hist_kernel(const int* __restrict__ topk_idx,
+                                                              int npairs, int E,
+                                                              int* __restrict__ chunk_counts) {
+    __shared__ int cnt[ROUTE_MAX_E];
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    const int i = blockIdx.x * PERM_CHUNK + threadIdx.x;
+    if (i < npairs) atomicAdd(&cnt[topk_idx[i]], 1);  // a count: order-independent
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) chunk_counts[static_cast<size_t>(blockIdx.x) * E + e] = cnt[e];
+}
+
+__global__ void __launch_bounds__(ROUTE_MAX_E) moe_scan_kernel(int* __restrict__ chunk_counts, int nchunks,
+                                                               int E, int pad, int seg,
+                                                               int* __restrict__ counts,
+                                                               int* __restrict__ offsets) {
+    __shared__ int padded[ROUTE_MAX_E];
+    const int e = threadIdx.x;
+    if (e < E) {
+        int run = 0;
+        for (int c = 0; c < nchunks; ++c) {  // exclusive scan over chunks, in place
+            const int v = chunk_counts[static_cast<size_t>(c) * E + e];
+            chunk_counts[static_cast<size_t>(c) * E + e] = run;
+            run += v;
+        }
+        counts[e] = run;
+        padded[e] = (run + pad - 1) / pad * pad;
+    }
+    __syncthreads();
+    if (e == 0) {
+        // offsets restart at every segment of `seg` experts (one segment per destination rank);
+        // offsets has E + E/seg entries: for segment g, entries [g*(seg+1), (g+1)*(seg+1))
+        const int nseg = E / seg;
+        for (int g = 0; g < nseg; ++g) {
+            int run = 0;
+            for (int j = 0; j < seg; ++j) {
+                offsets[g * (seg + 1) + j] = run;
+                run += padded[g * seg + j];
+            }
+            offsets[g * (seg + 1) + seg] = run;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(PERM_CHUNK) moe_place_kernel(const int* __restrict__ topk_idx, int npairs,
+                                                               int E, int seg,
+                                                               const int* __restrict__ chunk_base,
+                                                               const int* __restrict__ offsets,
+                                                               int* __restrict__ row_of_pair,
+                                                               int* __restrict__ pair_of_row,
+                                                               int seg_row_capacity) {
+    __shared__ int warp_cnt[PERM_CHUNK / 32][ROUTE_MAX_E];  // 32 KiB
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int x = threadIdx.x; x < (PERM_CHUNK / 32) * ROUTE_MAX_E; x += blockDim.x)
+        (&warp_cnt[0][0])[x] = 0;
+    __syncthreads();
+    const int i = blockIdx.x * PERM_CHUNK + threadIdx.x;
+    const bool live = i < npairs;
+    const int e = live ? topk_idx[i] : -1;
+    // lanes of this warp holding the same expert; my rank among them = those before me
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank_in_warp = __popc(peers & ((1u << lane) - 1));
+    if (live && rank_in_warp == 0) warp_cnt[warp][e] = __popc(peers);
+    __syncthreads();
+    if (live) {
+        int before = 0;
+        for (int w = 0; w < warp; ++w) before += warp_cnt[w][e];
+        const int g = e / seg;
+        const int row = offsets[g * (seg + 1) + (e - g * seg)] +
+                        chunk_base[static_cast<size_t>(blockIdx.x) * E + e] + before + rank_in_warp;
+        row_of_pair[i] = row;
+        pair_of_row[static_cast<size_t>(g) * seg_row_capacity + row] = i;
+    }
+}
+
+// ------------------------------------------------------------------------------------ quantise
+// One CTA per 128x128 block. 256 threads; thread t owns column chunk (t % 16) * 8 of rows
+// t/16 + 16*i, i = 0..7. Source rows come straight from x, or through a row map:
+//   map_mode 0: row r of x;  1: row map[r] / k of x (gather), zeros where map[r] < 0;
+//   2: row r of x where map[r] >= 0, zeros elsewhere (rows already in place, padding undefined)
+__global__ void __launch_bounds__(256) quant_block128_kernel(const __nv_bfloat16* __restrict__ x, int R, int C,
+                                                             const int* __restrict__ map, int map_mode,
+                                                             int k, uint8_t* __restrict__ q,
+                                                             float* __restrict__ s) {
+    __shared__ float red[8];
+    const int bc = blockIdx.x, br = blockIdx.y;
+    const int cchunk = (threadIdx.x & 15) * 8;
+    const int r0 = threadIdx.x >> 4;
+    float vals[8][8];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int r = br * 128 + r0 + 16 * i;
+        long src = r;
+        bool valid = true;
+        if (map_mode != 0) {
+            const int mv = map[r];
+            valid = mv >= 0;
+            if (map_mode == 1) src = valid ? mv / k : 0;
+        }
+        uint4 u = make_uint4(0, 0, 0, 0);
+        if (valid) u = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(src) * C + bc * 128 + cchunk);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            vals[i][2 * j] = f.x;
+            vals[i][2 * j + 1] = f.y;
+            amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
+    const float scale = amax > 0.f ? amax / 448.0f : 1.0f;
+    if (threadIdx.x == 0) s[static_cast<size_t>(br) * (C / 128) + bc] = scale;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int r = br * 128 + r0 + 16 * i;
+        uint8_t b[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float y = vals[i][j] / scale;  // IEEE division: same bits as the CPU definition
+            y = fminf(fmaxf(y, -448.0f), 448.0f);
+            b[j] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3));
+        }
+        *reinterpret_cast<uint2*>(q + static_cast<size_t>(r) * C + bc * 128 + cchunk) =
+            *reinterpret_cast<const uint2*>(b);
+    }
+}
+
+// ------------------------------------------------------------------------------------ combine
+// out[t, :] = sum_j w[t,j] * Y_j[row(t,j), :]. One block per token; y_base[j-th pair] selects the
+// buffer (this rank's Y, or a peer's Y in the expert-parallel case).
+struct CombineArgs {
+    const __nv_bfloat16* y[DK_MAX_RANKS];  // Y of rank r as seen from here
+    const int* row_of_pair;                // [T, k]
+    const int* dest_of_pair;               // [T, k] rank holding the row; null = all local (y[0])
+    const float* w;                        // [T, k]
+    __nv_bfloat16* out;                    // [T, H]
+    int T, k, H;
+};
+__global__ void __launch_bounds__(256) moe_combine_kernel(const CombineArgs a) {
+    const int t = blockIdx.x;
+    __shared__ int row_s[ROUTE_MAX_K];
+    __shared__ int dst_s[ROUTE_MAX_K];
+    __shared__ float w_s[ROUTE_MAX_K];
+    if (threadIdx.x < a.k) {
+        row_s[threadIdx.x] = a.row_of_pair[static_cast<size_t>(t) * a.k + threadIdx.x];
+        dst_s[threadIdx.x] = a.dest_of_pair ? a.dest_of_pair[static_cast<size_t>(t) * a.k + threadIdx.x] : 0;
+        w_s[threadIdx.x] = a.w[static_cast<size_t>(t) * a.k + threadIdx.x];
+    }
+    __syncthreads();
+    for (int c = threadIdx.x * 8; c < a.H; c += blockDim.x * 8) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int j = 0; j < a.k; ++j) {
+            const uint4 u = __ldcg(reinterpret_cast<const uint4*>(
+                a.y[dst_s[j]] + static_cast<size_t>(row_s[j]) * a.H + c));
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+            const float wj = w_s[j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(h[i]);
+                acc[2 * i] += wj * f.x;
+                acc[2 * i + 1] += wj * f.y;
+            }
+        }
+        uint4 o;
+        o.x = pack_bf16x2(acc[0], acc[1]);
+        o.y = pack_bf16x2(acc[2], acc[3]);
+        o.z = pack_bf16x2(acc[4], acc[5]);
+        o.w = pack_bf16x2(acc[6], acc[7]);
+        *reinterpret_cast<uint4*>(a.out + static_cast<size_t>(t) * a.H + c) = o;
+    }
+}
+
+// shared by the allocating and the non-allocating permute entry points
+int moe_permute_launch(const int* topk_idx, int T, int k, int E, int pad, int seg, int* row_of_pair,
+                       int* pair_of_row, int seg_row_capacity, int* offsets, int* counts,
+                       int* scratch, cudaStream_t st) {
+    const int npairs = T * k;
+    const int nseg = E / seg;
+    DK_CUDA_OK(cudaMemsetAsync(pair_of_row, 0xff, static_cast<size_t>(nseg) * seg_row_capacity * sizeof(int), st));
+    const int nchunks = (npairs + PERM_CHUNK - 1) / PERM_CHUNK;
+    if (nchunks > 0) {
+        moe_hist_kernel<<<nchunks, PERM_CHUNK, 0, st>>>(topk_idx, npairs, E, scratch);
+        DK_CUDA_OK(cudaGetLastError());
+    }
+    moe_scan_kernel<<<1, ROUTE_MAX_E, 0, st>>>(scratch, nchunks, E, pad, seg, counts, offsets);
+    DK_CUDA_OK(cudaGetLastError());
+    if (nchunks > 0) {
+        moe_place_kernel<<<nchunks, PERM_CHUNK, 0, st>>>(topk_idx, npairs, E, seg, scratch, offsets,
+                                                         row_of_pair, pair_of_row, seg_row_capacity);
+        DK_CUDA_OK(cudaGetLastError());
+    }
+    return DK_OK;
+}
+
+int moe_permute_check(const void* topk_idx, int T, int k, int E, int pad, int seg, const void* a,
+                      const void* b, const void* c, const void* d, int seg_row_capacity) {
+    DK_REQUIRE(T >= 0 && k >= 1 && k <= ROUTE_MAX_K, "k must be 1..8");
+    DK_REQUIRE(E >= 1 && E <= ROUTE_MAX_E, "E must be 1..256");
+    DK_REQUIRE(pad >= 1, "pad must be positive");
+    DK_REQUIRE(seg >= 1 && E % seg == 0, "experts per segment must divide E");
+    DK_REQUIRE((T == 0 || topk_idx != nullptr) && a && b && c && d, "null buffer");
+    DK_REQUIRE(seg_row_capacity >= 0, "negative capacity");
+    return DK_OK;
+}
+
+}  // namespace dk
+
+extern "C" {
+
+int dk_moe_route(const float* logits, int T, int E, int k, int* topk_idx, float* topk_w, void* stream) {
+    using namespace dk;
+    DK_REQUIRE(T >= 0 && E >= 1 && E <= ROUTE_MAX_E, "E must be 1..256");
+    DK_REQUIRE(k >= 1 && k <= ROUTE_MAX_K && k <= E, "k must be 1..8 and <= E");
+    if (T == 0) return DK_OK;
+    DK_REQUIRE(logits && topk_idx && topk_w, "null buffer");
+    const int warps_per_block = 8;
+    moe_route_kernel<<<(T + warps_per_block - 1) / warps_per_block, warps_per_block * 32, 0,
+                       static_cast<cudaStream_t>(stream)>>>(logits, T, E, k, topk_idx, topk_w);
+    DK_CUDA_OK(cudaGetLastError());
+    return DK_OK;
+}
+
+size_t dk_moe_permute_scratch_bytes(int T, int k, int E) {
+    if (T < 0 || k < 1 || E < 1) return 0;
+    const size_t nchunks = (static_cast<size_t>(T) * k + dk::PERM_CHUNK - 1) / dk::PERM_CHUNK;
+    return (nchunks > 0 ? nchunks : 1) * E * sizeof(int);
+}
+
+size_t dk_moe_rows_capacity(int T, int k, int E, int pad) {
+    if (T < 0 || k < 1 || E < 1 || pad < 1) return 0;
+    // every expert may waste up to pad-1 rows
+    const size_t cap = static_cast<size_t>(T) * k + static_cast<size_t>(E) * (pad - 1);
+    return (cap + pad - 1) / pad * pad;
+}
+
+int dk_moe_permute(const int* topk_idx, int T, int k, int E, int pad, int experts_per_segment,
+                   int* row_of_pair, int* pair_of_row, int seg_row_capacity, int* offsets,
+                   int* counts, void* scratch, size_t scratch_bytes, void* stream) {
+    using namespace dk;
+    int rc = moe_permute_check(topk_idx, T, k, E, pad, experts_per_segment, row_of_pair, pair_of_row,
+                               offsets, counts, seg_row_capacity);
+    if (rc != DK_OK) return rc;
+    DK_REQUIRE(scratch != nullptr && scratch_bytes >= dk_moe_permute_scratch_bytes(T, k, E),
+               "scratch too small: see dk_moe_permute_scratch_bytes");
+    return moe_permute_launch(topk_idx, T, k, E, pad, experts_per_segment, row_of_pair, pair_of_row,
+                              seg_row_capacity, offsets, counts, static_cast<int*>(scratch),
+                              static_cast<cudaStream_t>(stream));
+}
+
+int dk_quant_block128(const void* x, int R, int C, const int* row_map, int map_mode, int k, void* q,
+                      float* s, void* stream) {
+    using namespace dk;
+    DK_REQUIRE(R >= 0 && C > 0 && R % 128 == 0 && C % 128 == 0, "R and C must be multiples of 128");
+    DK_REQUIRE(map_mode >= 0 && map_mode <= 2, "map_mode must be 0, 1 or 2");
+    DK_REQUIRE(map_mode == 0 || row_map != nullptr, "row_map is null");
+    DK_REQUIRE(map_mode != 1 || k >= 1, "k must be positive");
+    if (R == 0) return DK_OK;
+    DK_REQUIRE(x && q && s, "null buffer");
+    quant_block128_kernel<<<dim3(C / 128, R / 128), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x), R, C, row_map, map_mode, k, static_cast<uint8_t*>(q), s);
+    DK_CUDA_OK(cudaGetLastError());
+    return DK_OK;
+}
+
+int dk_moe_combine(const void* y, const int* row_of_pair, const float* topk_w, int T, int k, int H,
+                   void* out, void* stream) {
+    using namespace dk;
+    DK_REQUIRE(T >= 0 && k >= 1 && k <= ROUTE_MAX_K && H > 0 && H % 8 == 0, "bad shape");
+    if (T == 0) return DK_OK;
+    DK_REQUIRE(y && row_of_pair && topk_w && out, "null buffer");
+    CombineArgs a{};
+    a.y[0] = static_cast<const __nv_bfloat16*>(y);
+    a.row_of_pair = row_of_pair;
+    a.dest_of_pair = nullptr;
+    a.w = topk_w;
+    a.out = static_cast<__nv_bfloat16*>(out);
+    a.T = T;
+    a.k = k;
+    a.H = H;
+    moe_combine_kernel<<<T, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    DK_CUDA_OK(cudaGetLastError());
+    return DK_OK;
+}
+
+}  // extern "C"

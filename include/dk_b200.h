@@ -158,6 +158,46 @@ int dk_allreduce(const void* x, void* out, size_t n, int algo, const dk_view* vi
 int dk_allreduce_all_ranks(int world, const dk_view* views, const void* const* x, void* const* out,
                            size_t n, int algo, unsigned epoch, void* stream);
 
+/* ------------------------------------------------------------------ MoE: routing, layout, fp8 */
+/*
+ * None of the MoE entry points has a counterpart in the reference (it contains no MoE code); the
+ * fp8 pieces follow the pattern of its block-scaled fixtures
+ * (tests/unit/cdna4/warp/register/tile/mma_scaled.cu:200-258) with 128x128 fp32 scale blocks.
+ *
+ * dk_moe_route: top-k of logits[T,E] (fp32, E <= 256, k <= 8) on the raw logits, ties to the lower
+ * expert index, slots in descending logit order; topk_w = softmax over all experts, gathered and
+ * renormalised to sum to one.
+ */
+int dk_moe_route(const float* logits, int T, int E, int k, int* topk_idx, float* topk_w, void* stream);
+/*
+ * dk_moe_permute: group the T*k (token, slot) pairs by expert, pairs of one expert in (token,
+ * slot) order, every expert padded to a multiple of `pad` rows. Experts are cut into segments of
+ * `experts_per_segment` (= E for one GPU; = E / world for expert parallelism, one segment per
+ * destination rank) and row numbering restarts in every segment.
+ *   row_of_pair [T*k]                      row of the pair inside its segment
+ *   pair_of_row [E/seg][seg_row_capacity]  inverse map, -1 on padding rows
+ *   offsets     [E/seg][seg+1]             first row of each expert inside its segment
+ *   counts      [E]                        pairs per expert
+ * scratch: dk_moe_permute_scratch_bytes(T, k, E) bytes of device memory.
+ * dk_moe_rows_capacity(T, k, E, pad): rows that always suffice for one segment.
+ */
+size_t dk_moe_permute_scratch_bytes(int T, int k, int E);
+size_t dk_moe_rows_capacity(int T, int k, int E, int pad);
+int dk_moe_permute(const int* topk_idx, int T, int k, int E, int pad, int experts_per_segment,
+                   int* row_of_pair, int* pair_of_row, int seg_row_capacity, int* offsets,
+                   int* counts, void* scratch, size_t scratch_bytes, void* stream);
+/*
+ * dk_quant_block128: x[*,C] bf16 -> q[R,C] e4m3 bytes + s[R/128, C/128] fp32, per 128x128 block
+ * s = amax/448 (1 if the block is all zero), q = round-to-nearest-even(clamp(x/s, +-448)).
+ * map_mode 0: row r of x. 1: row row_map[r]/k of x (gather of tokens into permuted rows), zeros
+ * where row_map[r] < 0. 2: row r of x where row_map[r] >= 0, zeros elsewhere.
+ */
+int dk_quant_block128(const void* x, int R, int C, const int* row_map, int map_mode, int k, void* q,
+                      float* s, void* stream);
+/* out[t,:] = sum_j topk_w[t,j] * y[row_of_pair[t,j], :] in fp32, bf16 out. H % 8 == 0. */
+int dk_moe_combine(const void* y, const int* row_of_pair, const float* topk_w, int T, int k, int H,
+                   void* out, void* stream);
+
 /* ------------------------------------------------------------------ device helpers */
 /* For hosts that link this library but not the CUDA runtime (the pybind11 modules). */
 int dk_device_set(int device);
