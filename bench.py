@@ -158,9 +158,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--shape", default=None, help="M,N,K override of the workload (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 0)
 
+    global M_TOK, N_OUT, K_FULL
+    if args.shape:
+        M_TOK, N_OUT, K_FULL = (int(v) for v in args.shape.split(","))
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", str(rank)))
@@ -255,35 +260,38 @@ def main():
     flop_total = 2.0 * M_TOK * N_OUT * K_FULL
     value = flop_total / (ms_step * 1e-3) / 1e12
 
-    # ---- end to end through the Python entry point with host operands
-    hA = torch.empty(M_TOK, Kloc, dtype=torch.bfloat16).pin_memory()
-    hB = torch.empty(N_OUT, Kloc, dtype=torch.bfloat16).pin_memory()
-    hA.copy_(sets[0][0])
-    hB.copy_(sets[0][1])
-    hO = torch.empty(Mloc, N_OUT, dtype=torch.bfloat16).pin_memory()
-    dA, dB = torch.empty_like(sets[0][0]), torch.empty_like(sets[0][1])
+    e2e_value = e2e_ms = None
+    h2d = d2h = 0
+    if not args.no_e2e:
+        # ---- end to end through the Python entry point with host operands
+        hA = torch.empty(M_TOK, Kloc, dtype=torch.bfloat16).pin_memory()
+        hB = torch.empty(N_OUT, Kloc, dtype=torch.bfloat16).pin_memory()
+        hA.copy_(sets[0][0])
+        hB.copy_(sets[0][1])
+        hO = torch.empty(Mloc, N_OUT, dtype=torch.bfloat16).pin_memory()
+        dA, dB = torch.empty_like(sets[0][0]), torch.empty_like(sets[0][1])
 
-    def e2e_step():
-        dA.copy_(hA, non_blocking=True)
-        dB.copy_(hB, non_blocking=True)
-        tk_kernel.gemm_rs(dA, dB, out, view)
-        hO.copy_(out, non_blocking=True)
+        def e2e_step():
+            dA.copy_(hA, non_blocking=True)
+            dB.copy_(hB, non_blocking=True)
+            tk_kernel.gemm_rs(dA, dB, out, view)
+            hO.copy_(out, non_blocking=True)
 
-    e2e_step()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.e2e_steps):
         e2e_step()
-    e1.record()
-    barrier()
-    te = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_ms = te.item() / args.e2e_steps
-    e2e_value = flop_total / (e2e_ms * 1e-3) / 1e12
-    h2d = (hA.numel() + hB.numel()) * 2
-    d2h = hO.numel() * 2
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.e2e_steps):
+            e2e_step()
+        e1.record()
+        barrier()
+        te = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e_ms = te.item() / args.e2e_steps
+        e2e_value = flop_total / (e2e_ms * 1e-3) / 1e12
+        h2d = (hA.numel() + hB.numel()) * 2
+        d2h = hO.numel() * 2
 
     if rank == 0:
         peaks, peak_src = load_peaks()

@@ -87,6 +87,7 @@ def _declare(L: C.CDLL) -> None:
     L.dk_moe_permute.argtypes = [vp, i, i, i, i, i, vp, vp, i, vp, vp, vp, sz, vp]
     L.dk_quant_block128.argtypes = [vp, i, i, vp, i, i, vp, vp, vp]
     L.dk_moe_combine.argtypes = [vp, vp, vp, i, i, i, vp, vp]
+    L.dk_moe_grouped_gemm_fp8.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, vp, vp, vp]
     L.dk_allreduce_all_ranks.argtypes = [i, C.POINTER(DkView), C.POINTER(vp), C.POINTER(vp), sz, i,
                                          C.c_uint, vp]
 
@@ -326,3 +327,30 @@ def moe_combine(y, row_of_pair, topk_w, stream=None):
     check(lib().dk_moe_combine(_ptr(y), _ptr(row_of_pair), _ptr(topk_w), T, k, H, _ptr(out),
                                _stream_ptr(stream)))
     return out
+
+
+def moe_grouped_gemm_fp8(xq, xs, wq, ws, offsets, gated: bool, stream=None):
+    """Grouped fp8 GEMM. gated: returns (hq uint8 [R,F], hs fp32 [R/128,F/128]); else Y bf16 [R,N].
+    Output rows beyond offsets[E] are zero-initialised here for convenience."""
+    import torch
+    _need_cuda(xq, xs, wq, ws, offsets)
+    R, K = xq.shape
+    E = wq.shape[0]
+    if gated:
+        N = wq.shape[1] // 2
+        out = torch.zeros((R, N), dtype=torch.uint8, device=xq.device)
+        sc = torch.ones((R // 128, N // 128), dtype=torch.float32, device=xq.device)
+    else:
+        N = wq.shape[1]
+        out = torch.zeros((R, N), dtype=torch.bfloat16, device=xq.device)
+        sc = None
+    check(lib().dk_moe_grouped_gemm_fp8(_ptr(xq), _ptr(xs), _ptr(wq), _ptr(ws), _ptr(offsets), E, R, N, K,
+                                        1 if gated else 0, _ptr(out), _ptr(sc) if sc is not None else None,
+                                        _stream_ptr(stream)))
+    return (out, sc) if gated else out
+
+
+def moe_ffn_fp8(xq, xs, w13q, w13s, w2q, w2s, offsets, stream=None):
+    """gate/up grouped GEMM + SiLU*mul + requantise, then the down grouped GEMM. Returns Y bf16 [R,H]."""
+    hq, hs = moe_grouped_gemm_fp8(xq, xs, w13q, w13s, offsets, True, stream)
+    return moe_grouped_gemm_fp8(hq, hs, w2q, w2s, offsets, False, stream)

@@ -308,7 +308,8 @@ int moe_permute_check(const void* topk_idx, int T, int k, int E, int pad, int se
     DK_REQUIRE(E >= 1 && E <= ROUTE_MAX_E, "E must be 1..256");
     DK_REQUIRE(pad >= 1, "pad must be positive");
     DK_REQUIRE(seg >= 1 && E % seg == 0, "experts per segment must divide E");
-    DK_REQUIRE((T == 0 || topk_idx != nullptr) && a && b && c && d, "null buffer");
+    DK_REQUIRE((T == 0 || (topk_idx != nullptr && a != nullptr)) && c && d, "null buffer");
+    DK_REQUIRE(b != nullptr || seg_row_capacity == 0, "null buffer");
     DK_REQUIRE(seg_row_capacity >= 0, "negative capacity");
     return DK_OK;
 }

@@ -198,6 +198,19 @@ int dk_quant_block128(const void* x, int R, int C, const int* row_map, int map_m
 int dk_moe_combine(const void* y, const int* row_of_pair, const float* topk_w, int T, int k, int H,
                    void* out, void* stream);
 
+/*
+ * dk_moe_grouped_gemm_fp8: per expert e, rows [offsets[e], offsets[e+1]) of X (multiples of 128,
+ * read on the device) times that expert's weight, e4m3 operands with 128x128 fp32 block scales
+ * (xs [R/128, K/128]; ws [E, rows/128, K/128]), fp32 accumulation with per-128-K promotion.
+ *   gated = 1: wq is [E, 2N, K] (N gate rows, then N up rows); out = e4m3 bytes [R, N] of
+ *              silu(gate) * up, requantised per 128x128 block, out_scales [R/128, N/128]. N % 128 == 0.
+ *   gated = 0: wq is [E, N, K]; out = bf16 [R, N]; out_scales unused. N % 256 == 0.
+ * Rows at or beyond offsets[E] are not written.
+ */
+int dk_moe_grouped_gemm_fp8(const void* xq, const float* xs, const void* wq, const float* ws,
+                            const int* offsets, int E, int R, int N, int K, int gated, void* out,
+                            float* out_scales, void* stream);
+
 /* ------------------------------------------------------------------ device helpers */
 /* For hosts that link this library but not the CUDA runtime (the pybind11 modules). */
 int dk_device_set(int device);

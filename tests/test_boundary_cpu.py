@@ -112,8 +112,7 @@ def _comm_worker(rank, world, name, q):
     rc2 = L.dk_comm_allgather_fd(c, fd, fds)
     seen = []
     for r in range(world):
-        os.lseek(fds[r], 0, os.SEEK_SET)
-        seen.append(os.read(fds[r], 8))
+        seen.append(os.pread(fds[r], 8, 0))   # the descriptors share one file offset: no seek
         os.close(fds[r])
     rc3 = L.dk_comm_barrier(c)
     L.dk_comm_destroy(c)
