@@ -86,6 +86,9 @@ def _declare(L: C.CDLL) -> None:
     L.dk_moe_rows_capacity.argtypes = [i, i, i, i]
     L.dk_moe_permute.argtypes = [vp, i, i, i, i, i, vp, vp, i, vp, vp, vp, sz, vp]
     L.dk_quant_block128.argtypes = [vp, i, i, vp, i, i, vp, vp, vp]
+    L.dk_moe_permute_static_max_bytes.restype = sz
+    L.dk_moe_permute_static_max_bytes.argtypes = []
+    L.dk_moe_permute_static.argtypes = [vp, i, i, i, i, i, vp, vp, i, vp, vp, vp]
     L.dk_moe_combine.argtypes = [vp, vp, vp, i, i, i, vp, vp]
     L.dk_moe_grouped_gemm_fp8.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, vp, vp, vp]
     L.dk_allreduce_all_ranks.argtypes = [i, C.POINTER(DkView), C.POINTER(vp), C.POINTER(vp), sz, i,

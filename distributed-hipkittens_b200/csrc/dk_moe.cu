@@ -15,6 +15,9 @@
 //   combine   out[t] = sum_j w[t,j] * Y[row(t,j)] in fp32, slot order
 #include <cuda_fp8.h>
 
+#include <mutex>
+#include <string>
+
 #include "dk_heap.h"
 #include "dk_host.h"
 #include "dk_ptx.cuh"
@@ -355,6 +358,53 @@ int dk_moe_permute(const int* topk_idx, int T, int k, int E, int pad, int expert
                "scratch too small: see dk_moe_permute_scratch_bytes");
     return moe_permute_launch(topk_idx, T, k, E, pad, experts_per_segment, row_of_pair, pair_of_row,
                               seg_row_capacity, offsets, counts, static_cast<int*>(scratch),
+                              static_cast<cudaStream_t>(stream));
+}
+
+// ---- permutation without any allocation ----------------------------------------------------------
+// Scratch for dk_moe_permute_static: the per-chunk histograms live in this fixed array instead of
+// in memory the caller allocates. Every GPU that loads the library holds these 256 KiB until the
+// process exits. In host code the symbol is only a stand-in; its device address is looked up once
+// per device with cudaGetSymbolAddress and that pointer is what the kernels receive.
+#define DK_PERMUTE_STATIC_MAX_BYTES (256u * 1024u)
+static __device__ __align__(256) int g_permute_scratch[DK_PERMUTE_STATIC_MAX_BYTES / sizeof(int)];
+static int* g_permute_scratch_addr[64] = {nullptr};
+static std::mutex g_permute_scratch_mu;
+
+size_t dk_moe_permute_static_max_bytes(void) { return DK_PERMUTE_STATIC_MAX_BYTES; }
+
+int dk_moe_permute_static(const int* topk_idx, int T, int k, int E, int pad, int experts_per_segment,
+                          int* row_of_pair, int* pair_of_row, int seg_row_capacity, int* offsets,
+                          int* counts, void* stream) {
+    using namespace dk;
+    int rc = moe_permute_check(topk_idx, T, k, E, pad, experts_per_segment, row_of_pair, pair_of_row,
+                               offsets, counts, seg_row_capacity);
+    if (rc != DK_OK) return rc;
+    const size_t need = dk_moe_permute_scratch_bytes(T, k, E);
+    if (need > DK_PERMUTE_STATIC_MAX_BYTES) {
+        set_last_error("argument error: this routing needs " + std::to_string(need) +
+                       " bytes of scratch, more than the " + std::to_string(DK_PERMUTE_STATIC_MAX_BYTES) +
+                       " bytes built into dk_moe_permute_static; use dk_moe_permute with caller scratch");
+        return DK_ERR_ARG;
+    }
+    int dev = 0;
+    DK_CUDA_OK(cudaGetDevice(&dev));
+    DK_REQUIRE(dev >= 0 && dev < 64, "device index out of range");
+    int* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_permute_scratch_mu);
+        if (g_permute_scratch_addr[dev] == nullptr) {
+            // first call on this device: resolve the array's address on the current device
+            void* p = nullptr;
+            DK_CUDA_OK(cudaGetSymbolAddress(&p, g_permute_scratch));
+            g_permute_scratch_addr[dev] = static_cast<int*>(p);
+        }
+        scratch = g_permute_scratch_addr[dev];
+    }
+    // Nothing has to be cleared: the histogram kernel writes every [chunk][expert] entry this call
+    // reads, so whatever an earlier call left behind is overwritten before use.
+    return moe_permute_launch(topk_idx, T, k, E, pad, experts_per_segment, row_of_pair, pair_of_row,
+                              seg_row_capacity, offsets, counts, scratch,
                               static_cast<cudaStream_t>(stream));
 }
 

@@ -187,6 +187,26 @@ int dk_moe_permute(const int* topk_idx, int T, int k, int E, int pad, int expert
                    int* row_of_pair, int* pair_of_row, int seg_row_capacity, int* offsets,
                    int* counts, void* scratch, size_t scratch_bytes, void* stream);
 /*
+ * dk_moe_permute_static: dk_moe_permute for callers that must not allocate and have no scratch
+ * buffer of their own to hand in -- code running where device allocation is off limits (inside a
+ * region that forbids cudaMalloc, or a host runtime that was given a fixed set of buffers and no
+ * allocator). It has no counterpart in the reference. Same arguments and results as
+ * dk_moe_permute minus the scratch pair: the scratch is a fixed array compiled into the library,
+ * dk_moe_permute_static_max_bytes() = 256 KiB per GPU, held from library load to process exit.
+ * Routings that need more (dk_moe_permute_scratch_bytes(T, k, E) above that, i.e. more than
+ * 65536 / E chunks of 1024 pairs) are rejected with DK_ERR_ARG and a message naming both sizes.
+ * The call makes no cudaMalloc/cudaFree and uses no allocating library routine; inputs and outputs
+ * are the caller's. The first call on each device looks up the array's device address (that device
+ * must be current); make that first call before any stream capture starts. All calls on one GPU
+ * share the one array, which keeps the previous call's contents (harmless: every entry a call reads
+ * is written by that call first); two calls whose kernels overlap on the GPU, e.g. on different
+ * streams, race on it and must be serialised by the caller.
+ */
+size_t dk_moe_permute_static_max_bytes(void);
+int dk_moe_permute_static(const int* topk_idx, int T, int k, int E, int pad, int experts_per_segment,
+                          int* row_of_pair, int* pair_of_row, int seg_row_capacity, int* offsets,
+                          int* counts, void* stream);
+/*
  * dk_quant_block128: x[*,C] bf16 -> q[R,C] e4m3 bytes + s[R/128, C/128] fp32, per 128x128 block
  * s = amax/448 (1 if the block is all zero), q = round-to-nearest-even(clamp(x/s, +-448)).
  * map_mode 0: row r of x. 1: row row_map[r]/k of x (gather of tokens into permuted rows), zeros
