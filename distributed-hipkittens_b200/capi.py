@@ -91,6 +91,10 @@ def _declare(L: C.CDLL) -> None:
     L.dk_moe_permute_static.argtypes = [vp, i, i, i, i, i, vp, vp, i, vp, vp, vp]
     L.dk_moe_combine.argtypes = [vp, vp, vp, i, i, i, vp, vp]
     L.dk_moe_grouped_gemm_fp8.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, vp, vp, vp]
+    L.dk_peer_barrier.argtypes = [C.POINTER(DkView), vp]
+    L.dk_allgather.argtypes = [vp, sz, vp, C.POINTER(DkView), vp]
+    L.dk_moe_dispatch.argtypes = [vp, vp, vp, i, i, i, i, vp, C.POINTER(DkView), i, vp]
+    L.dk_moe_combine_ep.argtypes = [vp, vp, vp, vp, i, i, i, i, vp, C.POINTER(DkView), i, vp]
     L.dk_allreduce_all_ranks.argtypes = [i, C.POINTER(DkView), C.POINTER(vp), C.POINTER(vp), sz, i,
                                          C.c_uint, vp]
 
@@ -357,3 +361,39 @@ def moe_ffn_fp8(xq, xs, w13q, w13s, w2q, w2s, offsets, stream=None):
     """gate/up grouped GEMM + SiLU*mul + requantise, then the down grouped GEMM. Returns Y bf16 [R,H]."""
     hq, hs = moe_grouped_gemm_fp8(xq, xs, w13q, w13s, offsets, True, stream)
     return moe_grouped_gemm_fp8(hq, hs, w2q, w2s, offsets, False, stream)
+
+
+# ---------------------------------------------------------------------------- expert parallel
+def peer_barrier(view: DkView, stream=None):
+    check(lib().dk_peer_barrier(C.byref(view), _stream_ptr(stream)))
+
+
+def allgather(mine, all_out, view: DkView, stream=None):
+    """all_out (in the heap) = concatenation over ranks of `mine`."""
+    _need_cuda(mine, all_out)
+    check(lib().dk_allgather(_ptr(mine), mine.numel() * mine.element_size(), _ptr(all_out), C.byref(view),
+                             _stream_ptr(stream)))
+    return all_out
+
+
+def moe_dispatch(x, topk_idx, row_of_pair, experts_per_rank: int, xrecv, view: DkView, sync: bool = True,
+                 stream=None):
+    _need_cuda(x, topk_idx, row_of_pair, xrecv)
+    T_loc, k = topk_idx.shape
+    check(lib().dk_moe_dispatch(_ptr(x), _ptr(topk_idx), _ptr(row_of_pair), T_loc, k, x.shape[1],
+                                experts_per_rank, _ptr(xrecv), C.byref(view), 1 if sync else 0,
+                                _stream_ptr(stream)))
+    return xrecv
+
+
+def moe_combine_ep(y, topk_idx, row_of_pair, topk_w, experts_per_rank: int, view: DkView, sync: bool = True,
+                   stream=None):
+    import torch
+    _need_cuda(y, topk_idx, row_of_pair, topk_w)
+    T_loc, k = topk_idx.shape
+    H = y.shape[1]
+    out = torch.empty((T_loc, H), dtype=torch.bfloat16, device=y.device)
+    check(lib().dk_moe_combine_ep(_ptr(y), _ptr(topk_idx), _ptr(row_of_pair), _ptr(topk_w), T_loc, k, H,
+                                  experts_per_rank, _ptr(out), C.byref(view), 1 if sync else 0,
+                                  _stream_ptr(stream)))
+    return out

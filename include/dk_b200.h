@@ -231,6 +231,36 @@ int dk_moe_grouped_gemm_fp8(const void* xq, const float* xs, const void* wq, con
                             const int* offsets, int E, int R, int N, int K, int gated, void* out,
                             float* out_scales, void* stream);
 
+/* ------------------------------------------------------------------ expert-parallel exchange */
+/*
+ * No counterpart in the reference (it has no all-to-all and no expert parallelism).
+ * Token t lives on rank t / T_loc; expert e on rank e / experts_per_rank. All of these are
+ * collective: every rank calls them in the same order.
+ *
+ * dk_peer_barrier: device-side barrier across the ranks of the view, ordered on `stream` (a
+ * one-block kernel: release-store of the heap's epoch into every peer's flag, bounded wait for
+ * theirs). Work enqueued before it on every rank is complete and visible after it on every rank.
+ * dk_allgather: all[r*bytes .. (r+1)*bytes) = rank r's `mine`, on every rank. `all` lies inside the
+ * heap (same offset everywhere); bytes % 16 == 0. Barriers before and after are included.
+ */
+int dk_peer_barrier(const dk_view* view, void* stream);
+int dk_allgather(const void* mine, size_t bytes, void* all, const dk_view* view, void* stream);
+/*
+ * dk_moe_dispatch: for each local token t and slot j, copy x[t, :] (H bf16) into row
+ * row_of_pair[t,j] of the receive buffer `xrecv` of rank topk_idx[t,j] / experts_per_rank (peer
+ * stores). row_of_pair is this rank's slice of the global permutation computed with one segment
+ * per rank (dk_moe_permute, experts_per_segment = experts_per_rank). xrecv lies inside the heap.
+ * sync != 0 brackets the copy with peer barriers (peers done with the old contents / all rows
+ * landed); sync == 0 leaves ordering to the caller.
+ * dk_moe_combine_ep: out[t,:] = sum_j topk_w[t,j] * y_of_rank(dest(t,j))[row_of_pair[t,j], :]
+ * with peer loads; y lies inside the heap; fp32 accumulation, bf16 out.
+ */
+int dk_moe_dispatch(const void* x, const int* topk_idx, const int* row_of_pair, int T_loc, int k, int H,
+                    int experts_per_rank, void* xrecv, const dk_view* view, int sync, void* stream);
+int dk_moe_combine_ep(const void* y, const int* topk_idx, const int* row_of_pair, const float* topk_w,
+                      int T_loc, int k, int H, int experts_per_rank, void* out, const dk_view* view,
+                      int sync, void* stream);
+
 /* ------------------------------------------------------------------ device helpers */
 /* For hosts that link this library but not the CUDA runtime (the pybind11 modules). */
 int dk_device_set(int device);

@@ -58,10 +58,45 @@ def _worker(rank, world, job, q):
             torch.cuda.synchronize()
             res[f"allreduce{algo}"] = orc.rel_fro(o.float().cpu(), ref)
             res[f"allreduce{algo}_sum"] = int(o.view(torch.int16).to(torch.int64).sum().item())
+        # ---- expert-parallel MoE layer: all-gather of the routing table, dispatch, FFN, combine
+        from __graft_entry__ import load_package
+        capi = load_package().capi
+        v = capi.DkView.from_address(view._addr())
+        T, H, F, E, k = 128 * world, 256, 128, 4 * world, 2
+        epr, Tl = E // world, T // world
+        x, logits, w13q, w13s, w2q, w2s = orc.make_moe_inputs(T, H, F, E, k, seed=5, zipf_s=1.1)
+        idx_c, w_c = orc.moe_route(logits, k)
+        rop_c, por_c, offs_c, _ = orc.moe_permute(idx_c, E)
+        xq_c, xs_c = orc.quant_block128(orc.moe_gather_rows(x, por_c, k))
+        y_c, _, _ = orc.moe_ffn_ref(xq_c, xs_c, w13q, w13s, w2q, w2s, offs_c)
+        want_moe = orc.moe_combine_ref(y_c, rop_c, w_c)[rank * Tl:(rank + 1) * Tl]
+        sl = slice(rank * Tl, (rank + 1) * Tl)
+        my_idx, my_w = capi.moe_route(logits[sl].contiguous().cuda(), k)
+        all_idx = torch.as_tensor(iris.empty([T, k], "int32"), device="cuda")
+        cap = capi.lib().dk_moe_rows_capacity(T, k, epr, 128)
+        xrecv = torch.as_tensor(iris.empty([cap, H]), device="cuda").view(torch.bfloat16)
+        ybuf = torch.as_tensor(iris.empty([cap, H]), device="cuda").view(torch.bfloat16)
+        moe_errs = []
+        for _ in range(2):
+            xrecv.fill_(33.0)
+            capi.allgather(my_idx, all_idx, v)
+            rop, por, offs, counts = capi.moe_permute(all_idx, E, 128, experts_per_segment=epr)
+            my_rop = rop[sl].contiguous()
+            capi.moe_dispatch(x[sl].contiguous().cuda(), my_idx, my_rop, epr, xrecv, v, sync=True)
+            xq, xs = capi.quant_block128(xrecv, row_map=por[rank].contiguous(), map_mode=2)
+            es = slice(rank * epr, (rank + 1) * epr)
+            y = capi.moe_ffn_fp8(xq, xs, w13q[es].cuda(), w13s[es].cuda(), w2q[es].cuda(), w2s[es].cuda(),
+                                 offs[rank].contiguous())
+            ybuf.copy_(y)
+            out_moe = capi.moe_combine_ep(ybuf, my_idx, my_rop, my_w, epr, v, sync=True)
+            torch.cuda.synchronize()
+            moe_errs.append(orc.rel_fro(out_moe.float().cpu(), want_moe))
+        res["moe_ep"] = moe_errs
+        res["moe_idx_ok"] = bool(torch.equal(all_idx.cpu(), idx_c))
         res["status"] = tk_kernel.device_status()
         iris.barrier()
         q.put((rank, res))
-        del out, x, o, view
+        del out, x, o, view, all_idx, xrecv, ybuf
         del iris
     except Exception as e:  # report instead of hanging the parent
         import traceback
@@ -86,6 +121,8 @@ def test_peer_memory_path(world):
         assert "error" not in results[r], results[r].get("error")
         assert results[r]["status"][0] == 0
         assert all(e <= 1e-2 for e in results[r]["gemm_rs"]), results[r]["gemm_rs"]
+        assert results[r]["moe_idx_ok"]
+        assert all(e <= 2e-2 for e in results[r]["moe_ep"]), results[r]["moe_ep"]
         for algo in (0, 1, -1):
             assert results[r][f"allreduce{algo}"] <= 1e-2
             # every rank holds the same bits
