@@ -46,7 +46,9 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock and throttle reasons with nvidia-smi. It is started well before the timed
+    region (its start-up is slow on multi-GPU hosts and would disturb the first steps); only
+    samples whose arrival time falls inside [t0, t1] are reported."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
@@ -69,9 +71,12 @@ class ClockSampler:
 
     def _read(self):
         for ln in self.proc.stdout:
-            self.lines.append(ln.strip())
+            self.lines.append((time.time(), ln.strip()))
 
-    def stop(self):
+    def count_in(self, t0, t1):
+        return sum(1 for (t, _) in self.lines if t0 <= t <= t1)
+
+    def stop(self, t0, t1):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -81,7 +86,9 @@ class ClockSampler:
             pass
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        for (t, ln) in self.lines:
+            if not (t0 <= t <= t1):
+                continue
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 6:
                 continue
@@ -215,13 +222,18 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
-        step(i)
-    barrier()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
+        t_wait = time.time() + 8.0
+        while not sampler.lines and time.time() < t_wait:   # let nvidia-smi finish starting up
+            time.sleep(0.05)
+    barrier()
+    for i in range(args.warmup):
+        step(i)
+    barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_clock0 = time.time()
     ev0.record()
     for i in range(args.steps):
         step(i)
@@ -229,7 +241,7 @@ def main():
     barrier()
     ms_total = ev0.elapsed_time(ev1)
     clocks_extended = False
-    if sampler and len(sampler.lines) < 4:
+    if sampler and sampler.count_in(t_clock0, time.time()) < 4:
         # the timed region was shorter than a few sampling periods: keep the same load running,
         # untimed, until the sampler has seen it
         clocks_extended = True
@@ -248,7 +260,7 @@ def main():
         extra += 10
         torch.cuda.synchronize()
     barrier()
-    clocks = sampler.stop() if sampler else None
+    clocks = sampler.stop(t_clock0, time.time()) if sampler else None
     if clocks is not None:
         clocks["extended_by_untimed_steps"] = extra if clocks_extended else 0
     status = tk_kernel.device_status()

@@ -42,6 +42,7 @@ struct ARJob {
     unsigned epoch;
     size_t nvec;             // 16-byte vectors (8 bf16) per rank input
     unsigned* status;
+    unsigned long long peer_wait_ns;
 };
 
 enum : unsigned { SITE_AR_START = 16, SITE_AR_END = 17 };
@@ -84,7 +85,7 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_kernel(const __grid_cons
     const int world = job.world;
     const int b = blockIdx.x;
     if (threadIdx.x == 0) abort_sm = 0;
-    const WaitCtx wc{job.status, &abort_sm};
+    const WaitCtx wc{job.status, &abort_sm, job.peer_wait_ns};
 
     // every peer has entered the kernel, so its input is complete
     if (!block_meet(me, world, DK_CTRL_AR_START, b, job.epoch, wc, SITE_AR_START)) return;
@@ -184,6 +185,7 @@ extern "C" int dk_allreduce(const void* x, void* out, size_t n, int algo, const 
     job.epoch = heap_next_epoch(static_cast<dk_heap*>(view->heap));
     rc = device_status_ptr(&job.status);
     if (rc != DK_OK) return rc;
+    job.peer_wait_ns = peer_wait_ns();
     ARRank& me = job.r[0];
     me.rank = view->rank;
     for (int r = 0; r < world; ++r) {
@@ -218,6 +220,7 @@ extern "C" int dk_allreduce_all_ranks(int world, const dk_view* views, const voi
     job.epoch = epoch;
     rc = device_status_ptr(&job.status);
     if (rc != DK_OK) return rc;
+    job.peer_wait_ns = peer_wait_ns();
     for (int q = 0; q < world; ++q) {
         const dk_view* v = &views[q];
         DK_REQUIRE(v->rank == q && v->world == world, "views must be ordered by rank");

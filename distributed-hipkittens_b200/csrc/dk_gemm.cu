@@ -71,6 +71,7 @@ struct GemmArgs {
     __nv_bfloat16* red_out;        // [rows_per_rank][N]
     const unsigned* red_flags;     // local flags [tiles_per_shard][world]
     unsigned* status;
+    unsigned long long peer_wait_ns;
 };
 
 enum : unsigned {
@@ -115,7 +116,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const WaitCtx wc{g.status, abort_sm};
+    const WaitCtx wc{g.status, abort_sm, g.peer_wait_ns};
     const int num_tiles = g.tiles_m * g.tiles_n;
     const bool do_gemm = (g.phases & 1) != 0;
 
@@ -447,6 +448,7 @@ int gemm_bf16_impl(const void* A, const void* Bt, void* C, int M, int N, int K, 
     g.epoch = 0;
     rc = device_status_ptr(&g.status);
     if (rc != DK_OK) return rc;
+    g.peer_wait_ns = peer_wait_ns();
     int sms = 0;
     rc = sm_count(&sms);
     if (rc != DK_OK) return rc;
@@ -527,6 +529,7 @@ int gemm_rs_impl(const void* A, const void* Bt, void* out, int M, int N, int Klo
     g.red_flags = reinterpret_cast<const unsigned*>(ws_local + flags_off);
     rc = device_status_ptr(&g.status);
     if (rc != DK_OK) return rc;
+    g.peer_wait_ns = peer_wait_ns();
     int sms = 0;
     rc = sm_count(&sms);
     if (rc != DK_OK) return rc;

@@ -2,6 +2,7 @@
 // the device status record.
 #include "dk_host.h"
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -133,9 +134,29 @@ int sm_count(int* out) {
     return DK_OK;
 }
 
+static std::mutex g_wait_mu;
+static long long g_peer_wait_ms = -1;
+unsigned long long peer_wait_ns() {
+    std::lock_guard<std::mutex> lk(g_wait_mu);
+    if (g_peer_wait_ms < 0) {
+        const char* e = std::getenv("DK_PEER_WAIT_MS");
+        g_peer_wait_ms = (e && *e) ? std::atoll(e) : 20000;
+        if (g_peer_wait_ms < 1) g_peer_wait_ms = 1;
+    }
+    return static_cast<unsigned long long>(g_peer_wait_ms) * 1000000ull;
+}
+
 }  // namespace dk
 
 extern "C" {
+
+int dk_set_peer_wait_ms(int ms) {
+    if (ms < 1) return DK_ERR_ARG;
+    std::lock_guard<std::mutex> lk(dk::g_wait_mu);
+    dk::g_peer_wait_ms = ms;
+    return DK_OK;
+}
+
 
 const char* dk_strerror(int code) {
     switch (code) {

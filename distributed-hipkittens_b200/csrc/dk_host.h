@@ -81,4 +81,8 @@ int device_status_ptr(unsigned** dev_ptr);
 
 int sm_count(int* out);
 
+// Limit of device-side waits on a signal from another rank, in nanoseconds
+// (DK_PEER_WAIT_MS, default 20 s).
+unsigned long long peer_wait_ns();
+
 }  // namespace dk

@@ -27,13 +27,14 @@ struct BarrierArgs {
     int rank, world;
     unsigned epoch;
     unsigned* status;
+    unsigned long long peer_wait_ns;
 };
 
 __global__ void __launch_bounds__(32) peer_barrier_kernel(const BarrierArgs a) {
     __shared__ int abort_sm;
     if (threadIdx.x == 0) abort_sm = 0;
     __syncwarp();
-    const WaitCtx wc{a.status, &abort_sm};
+    const WaitCtx wc{a.status, &abort_sm, a.peer_wait_ns};
     if (threadIdx.x < a.world) {
         const int r = threadIdx.x;
         __threadfence_system();
@@ -126,16 +127,17 @@ __global__ void __launch_bounds__(256) moe_combine_ep_kernel(const CombineEpArgs
     }
 }
 
-static int launch_peer_barrier(const dk_view* view, cudaStream_t st) {
+static int launch_peer_barrier(const dk_view* view, cudaStream_t st, unsigned explicit_epoch = 0) {
     if (view == nullptr || view->world <= 1) return DK_OK;
-    DK_REQUIRE(view->heap != nullptr, "view has no heap handle");
+    DK_REQUIRE(view->heap != nullptr || explicit_epoch != 0, "view has no heap handle");
     BarrierArgs a{};
     a.rank = view->rank;
     a.world = view->world;
-    a.epoch = heap_next_epoch(static_cast<dk_heap*>(view->heap));
+    a.epoch = explicit_epoch ? explicit_epoch : heap_next_epoch(static_cast<dk_heap*>(view->heap));
     for (int r = 0; r < view->world; ++r) a.ctrl[r] = ctrl_words(view, r);
     int rc = device_status_ptr(&a.status);
     if (rc != DK_OK) return rc;
+    a.peer_wait_ns = peer_wait_ns();
     peer_barrier_kernel<<<1, 32, 0, st>>>(a);
     DK_CUDA_OK(cudaGetLastError());
     return DK_OK;
@@ -155,6 +157,11 @@ extern "C" {
 
 int dk_peer_barrier(const dk_view* view, void* stream) {
     return dk::launch_peer_barrier(view, static_cast<cudaStream_t>(stream));
+}
+
+int dk_peer_barrier_epoch(const dk_view* view, unsigned epoch, void* stream) {
+    DK_REQUIRE(epoch != 0, "epochs start at 1");
+    return dk::launch_peer_barrier(view, static_cast<cudaStream_t>(stream), epoch);
 }
 
 int dk_allgather(const void* mine, size_t bytes, void* all, const dk_view* view, void* stream) {

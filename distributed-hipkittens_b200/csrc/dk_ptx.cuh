@@ -82,6 +82,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 struct WaitCtx {
     unsigned* status;        // 4 words in host-mapped memory (may be null)
     volatile int* abort_sm;  // CTA-wide abort flag in shared memory
+    // Limit for waits on ANOTHER GPU's signal. These also absorb host-side skew between ranks
+    // (a peer whose launch is late), so the limit is a run-time setting, far above the limit for
+    // waits inside one CTA.
+    unsigned long long peer_limit_ns = 20000000000ull;
 };
 
 enum : unsigned { DK_DEV_OK = 0, DK_DEV_TIMEOUT = 1, DK_DEV_PEER_TIMEOUT = 2 };
@@ -343,7 +347,7 @@ __device__ __forceinline__ bool signal_wait_ge(const unsigned* p, unsigned targe
     while (static_cast<int>(signal_load_acquire_sys(p) - target) < 0) {
         if ((++spins & 0x3f) == 0) {
             if (*w.abort_sm) return false;
-            if (globaltimer_ns() - t0 > DK_WAIT_LIMIT_NS) {
+            if (globaltimer_ns() - t0 > w.peer_limit_ns) {
                 record_timeout(w, DK_DEV_PEER_TIMEOUT, site, detail);
                 return false;
             }

@@ -60,6 +60,14 @@ int dk_version(void);
  * The reference has no counterpart (HIP errors are printed and dropped, include/pyutils/util.cuh:10-16).
  */
 int dk_last_device_status(unsigned out[4]);
+/*
+ * Limit, in milliseconds, of device-side waits on another rank's signal (flags of the
+ * reduce-scatter, all-reduce and peer barrier). Such a wait also covers the time by which a peer's
+ * launch lags behind on the host, so the default is generous: 20 s, or DK_PEER_WAIT_MS from the
+ * environment. When it runs out the kernel records {code 2, block, site, detail}, stops waiting and
+ * returns; the context stays usable. Applies to launches made after the call.
+ */
+int dk_set_peer_wait_ms(int ms);
 
 /* ------------------------------------------------------------------ symmetric heap */
 /*
@@ -244,6 +252,8 @@ int dk_moe_grouped_gemm_fp8(const void* xq, const float* xs, const void* wq, con
  * heap (same offset everywhere); bytes % 16 == 0. Barriers before and after are included.
  */
 int dk_peer_barrier(const dk_view* view, void* stream);
+/* The same with an explicit 1-based epoch, for views that carry no heap handle. */
+int dk_peer_barrier_epoch(const dk_view* view, unsigned epoch, void* stream);
 int dk_allgather(const void* mine, size_t bytes, void* all, const dk_view* view, void* stream);
 /*
  * dk_moe_dispatch: for each local token t and slot j, copy x[t, :] (H bf16) into row

@@ -68,3 +68,33 @@ def test_ep_layer_all_ranks_on_one_gpu(capi, orc, P, T, H, F, E, k, zipf):
     assert capi.device_status()[0] == 0
     got = torch.cat(outs, 0).float().cpu()
     assert orc.rel_fro(got, want) <= TOL
+
+
+def test_peer_wait_runs_out_and_is_reported(capi):
+    """Failure detection on the device without faulting it: a barrier with a peer that never
+    signals (a flag nothing sets) gives up after the configured limit, records where, and returns;
+    the context stays usable."""
+    import ctypes as C
+    region = capi.CTRL_BYTES + 4096
+    buf = torch.zeros(2 * region + 4096, dtype=torch.uint8, device="cuda")
+    base0 = (buf.data_ptr() + 1023) // 1024 * 1024
+    views = [capi.make_view(r, 2, [base0, base0 + region], region) for r in range(2)]
+    L = capi.lib()
+    capi.device_status()
+    capi.check(L.dk_set_peer_wait_ms(200))
+    try:
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        capi.check(L.dk_peer_barrier_epoch(C.byref(views[0]), 1, stream))    # rank 1 never arrives
+        torch.cuda.synchronize()
+        code, block, site, detail = capi.device_status()
+        assert code == 2 and site == 48 and detail == 1
+        # both ranks arrive (one after the other: the first leaves its flag, the second finds it)
+        capi.check(L.dk_peer_barrier_epoch(C.byref(views[1]), 1, stream))
+        torch.cuda.synchronize()
+        assert capi.device_status()[0] == 0
+    finally:
+        capi.check(L.dk_set_peer_wait_ms(20000))
+    a = torch.ones(128, 64, dtype=torch.bfloat16, device="cuda")
+    c = capi.gemm_bf16(a, a)
+    torch.cuda.synchronize()
+    assert float(c[0, 0]) == 64.0
