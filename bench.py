@@ -325,7 +325,9 @@ def main():
             "data": "synthetic",
             "config": {"workload": f"gemm_rs M={M_TOK} N={N_OUT} K={K_FULL} K-sharded over {P} GPU(s), "
                                    f"out rows reduce-scattered (Llama-70B MLP down-proj shape)",
-                       "l2": f"{nsets} operand sets of {shard_bytes / 1e6:.0f} MB rotated; each exceeds the 126 MB L2",
+                       "l2": f"{nsets} operand sets of {shard_bytes / 1e6:.0f} MB rotated: "
+                             f"{(nsets - 1) * shard_bytes / 1e6:.0f} MB of other operands pass between two "
+                             f"uses of a set (L2 is 126 MB)",
                        "per_gpu_tflops": value / P},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak if peak else None, "traffic": traffic,

@@ -136,6 +136,124 @@ void allreduce(py::object X, py::object Out, py::object view, int algo) {
              "allreduce");
 }
 
+// ---- MoE entry points. Outputs are torch tensors created through torch's Python API.
+py::object torch_empty(std::vector<int64_t> shape, const char* dtype, const py::object& like) {
+    py::object torch = py::module_::import("torch");
+    py::tuple shp(shape.size());
+    for (size_t i = 0; i < shape.size(); ++i) shp[i] = py::int_(shape[i]);
+    return torch.attr("empty")(shp, py::arg("dtype") = torch.attr(dtype), py::arg("device") = like.attr("device"));
+}
+void* tptr(const py::object& t) { return reinterpret_cast<void*>(t.attr("data_ptr")().cast<uint64_t>()); }
+
+py::tuple moe_route(py::object logits, int k) {
+    TensorArg l = tensor_arg(logits, "torch.float32");
+    if (l.shape.size() != 2) throw std::runtime_error("logits must be [T, E]");
+    const int T = static_cast<int>(l.shape[0]), E = static_cast<int>(l.shape[1]);
+    py::object idx = torch_empty({T, k}, "int32", logits);
+    py::object w = torch_empty({T, k}, "float32", logits);
+    throw_on(dk_moe_route(static_cast<const float*>(l.ptr), T, E, k, static_cast<int*>(tptr(idx)),
+                          static_cast<float*>(tptr(w)), current_stream()), "moe_route");
+    return py::make_tuple(idx, w);
+}
+
+py::tuple moe_permute(py::object topk_idx, int E, int pad, int experts_per_segment) {
+    TensorArg ti = tensor_arg(topk_idx, "torch.int32");
+    if (ti.shape.size() != 2) throw std::runtime_error("topk_idx must be [T, k]");
+    const int T = static_cast<int>(ti.shape[0]), k = static_cast<int>(ti.shape[1]);
+    const int seg = experts_per_segment > 0 ? experts_per_segment : E;
+    if (seg < 1 || E % seg != 0) throw std::runtime_error("experts_per_segment must divide E");
+    const int nseg = E / seg;
+    const int64_t cap = static_cast<int64_t>(dk_moe_rows_capacity(T, k, seg, pad));
+    py::object rop = torch_empty({T, k}, "int32", topk_idx);
+    py::object por = torch_empty({nseg, cap}, "int32", topk_idx);
+    py::object offs = torch_empty({nseg, seg + 1}, "int32", topk_idx);
+    py::object counts = torch_empty({E}, "int32", topk_idx);
+    const size_t sb = dk_moe_permute_scratch_bytes(T, k, E);
+    py::object scratch = torch_empty({static_cast<int64_t>(sb)}, "uint8", topk_idx);
+    throw_on(dk_moe_permute(static_cast<const int*>(ti.ptr), T, k, E, pad, seg, static_cast<int*>(tptr(rop)),
+                            static_cast<int*>(tptr(por)), static_cast<int>(cap), static_cast<int*>(tptr(offs)),
+                            static_cast<int*>(tptr(counts)), tptr(scratch), sb, current_stream()),
+             "moe_permute");
+    if (nseg == 1) return py::make_tuple(rop, por[py::int_(0)], offs[py::int_(0)], counts);
+    return py::make_tuple(rop, por, offs, counts);
+}
+
+py::tuple moe_quant(py::object X, py::object row_map, int map_mode, int k) {
+    TensorArg x = tensor_arg(X, "torch.bfloat16");
+    if (x.shape.size() != 2) throw std::runtime_error("X must be [rows, C]");
+    const int C = static_cast<int>(x.shape[1]);
+    int R = static_cast<int>(x.shape[0]);
+    const int* map = nullptr;
+    if (!row_map.is_none()) {
+        TensorArg m = tensor_arg(row_map, "torch.int32");
+        map = static_cast<const int*>(m.ptr);
+        R = static_cast<int>(m.numel());
+        if (map_mode == 0) map_mode = 1;
+    }
+    py::object q = torch_empty({R, C}, "uint8", X);
+    py::object s = torch_empty({R / 128, C / 128}, "float32", X);
+    throw_on(dk_quant_block128(x.ptr, R, C, map, map_mode, k, tptr(q), static_cast<float*>(tptr(s)),
+                               current_stream()), "moe_quant");
+    return py::make_tuple(q, s);
+}
+
+py::object moe_ffn_fp8(py::object Xq, py::object Xs, py::object W13q, py::object W13s, py::object W2q,
+                       py::object W2s, py::object offsets) {
+    TensorArg xq = tensor_arg(Xq, "torch.uint8"), xs = tensor_arg(Xs, "torch.float32");
+    TensorArg w13q = tensor_arg(W13q, "torch.uint8"), w13s = tensor_arg(W13s, "torch.float32");
+    TensorArg w2q = tensor_arg(W2q, "torch.uint8"), w2s = tensor_arg(W2s, "torch.float32");
+    TensorArg off = tensor_arg(offsets, "torch.int32");
+    if (xq.shape.size() != 2 || w13q.shape.size() != 3 || w2q.shape.size() != 3)
+        throw std::runtime_error("expected Xq [R,H], W13q [E,2F,H], W2q [E,H,F]");
+    const int R = static_cast<int>(xq.shape[0]), H = static_cast<int>(xq.shape[1]);
+    const int E = static_cast<int>(w13q.shape[0]), F = static_cast<int>(w13q.shape[1] / 2);
+    if (w13q.shape[2] != H || w2q.shape[0] != E || w2q.shape[1] != H || w2q.shape[2] != F || off.numel() != E + 1)
+        throw std::runtime_error("MoE weight / offset shapes disagree");
+    py::object hq = torch_empty({R, F}, "uint8", Xq);
+    py::object hs = torch_empty({R / 128, F / 128}, "float32", Xq);
+    py::object y = torch_empty({R, H}, "bfloat16", Xq);
+    void* st = current_stream();
+    throw_on(dk_moe_grouped_gemm_fp8(xq.ptr, static_cast<const float*>(xs.ptr), w13q.ptr,
+                                     static_cast<const float*>(w13s.ptr), static_cast<const int*>(off.ptr), E, R,
+                                     F, H, 1, tptr(hq), static_cast<float*>(tptr(hs)), st), "moe_ffn_fp8 (gate/up)");
+    throw_on(dk_moe_grouped_gemm_fp8(tptr(hq), static_cast<const float*>(tptr(hs)), w2q.ptr,
+                                     static_cast<const float*>(w2s.ptr), static_cast<const int*>(off.ptr), E, R,
+                                     H, F, 0, tptr(y), nullptr, st), "moe_ffn_fp8 (down)");
+    return y;
+}
+
+void moe_dispatch(py::object X, py::object topk_idx, py::object row_of_pair, int experts_per_rank,
+                  py::object Xrecv, py::object view) {
+    TensorArg x = tensor_arg(X, "torch.bfloat16"), ti = tensor_arg(topk_idx, "torch.int32");
+    TensorArg rp = tensor_arg(row_of_pair, "torch.int32"), xr = tensor_arg(Xrecv, "torch.bfloat16");
+    if (x.shape.size() != 2 || ti.shape.size() != 2 || rp.numel() != ti.numel())
+        throw std::runtime_error("expected X [T_loc,H], topk_idx [T_loc,k], row_of_pair [T_loc,k]");
+    throw_on(dk_moe_dispatch(x.ptr, static_cast<const int*>(ti.ptr), static_cast<const int*>(rp.ptr),
+                             static_cast<int>(ti.shape[0]), static_cast<int>(ti.shape[1]),
+                             static_cast<int>(x.shape[1]), experts_per_rank, xr.ptr, view_arg(view), 1,
+                             current_stream()), "moe_dispatch");
+}
+
+py::object moe_combine(py::object Y, py::object topk_idx, py::object row_of_pair, py::object topk_w,
+                       int experts_per_rank, py::object view) {
+    TensorArg y = tensor_arg(Y, "torch.bfloat16"), ti = tensor_arg(topk_idx, "torch.int32");
+    TensorArg rp = tensor_arg(row_of_pair, "torch.int32"), w = tensor_arg(topk_w, "torch.float32");
+    if (y.shape.size() != 2 || ti.shape.size() != 2 || rp.numel() != ti.numel() || w.numel() != ti.numel())
+        throw std::runtime_error("expected Y [R,H], topk_idx / row_of_pair / topk_w [T_loc,k]");
+    const int T = static_cast<int>(ti.shape[0]), k = static_cast<int>(ti.shape[1]), H = static_cast<int>(y.shape[1]);
+    py::object out = torch_empty({T, H}, "bfloat16", Y);
+    const dk_view* v = view_arg(view);
+    if (v == nullptr || v->world <= 1) {
+        throw_on(dk_moe_combine(y.ptr, static_cast<const int*>(rp.ptr), static_cast<const float*>(w.ptr), T, k, H,
+                                tptr(out), current_stream()), "moe_combine");
+    } else {
+        throw_on(dk_moe_combine_ep(y.ptr, static_cast<const int*>(ti.ptr), static_cast<const int*>(rp.ptr),
+                                   static_cast<const float*>(w.ptr), T, k, H, experts_per_rank, tptr(out), v, 1,
+                                   current_stream()), "moe_combine");
+    }
+    return out;
+}
+
 py::tuple device_status() {
     unsigned st[4] = {0, 0, 0, 0};
     throw_on(dk_last_device_status(st), "device_status");
@@ -153,6 +271,16 @@ PYBIND11_MODULE(tk_kernel, m) {
           "Out[M/P,N] = reduce-scatter over ranks of A[M,K/P] @ Bt[N,K/P]^T. Positional: A, Bt, Out, view");
     m.def("allreduce", &allreduce, py::arg("X"), py::arg("Out"), py::arg("view"), py::arg("algo") = -1,
           "Out = sum over ranks of X (bf16). algo: -1 auto, 0 one-shot, 1 two-shot, 2 NVLS");
+    m.def("moe_route", &moe_route, "(topk_idx int32 [T,k], topk_w fp32 [T,k]) from fp32 logits [T,E]");
+    m.def("moe_permute", &moe_permute, py::arg("topk_idx"), py::arg("E"), py::arg("pad") = 128,
+          py::arg("experts_per_segment") = 0,
+          "(row_of_pair, pair_of_row, expert_offsets, counts), int32, deterministic");
+    m.def("moe_quant", &moe_quant, py::arg("X"), py::arg("row_map") = py::none(), py::arg("map_mode") = 0,
+          py::arg("k") = 1, "(Xq e4m3 bytes, Xs fp32) with 128x128 block scales; optional row gather");
+    m.def("moe_ffn_fp8", &moe_ffn_fp8,
+          "Y[R,H] bf16 from Xq, Xs, W13q[E,2F,H], W13s, W2q[E,H,F], W2s, expert_offsets");
+    m.def("moe_dispatch", &moe_dispatch, "push local tokens into the destination ranks' receive rows");
+    m.def("moe_combine", &moe_combine, "Out[T_loc,H] = sum_j w_j * Y_dest[row_j]; pulls from peers when world > 1");
     m.def("device_status", &device_status,
           "(code, block, site, detail) of the first device-side wait that gave up; clears it");
 }

@@ -76,3 +76,31 @@ def test_grouped_gemm_empty_experts_and_errors(capi, orc):
     with pytest.raises(capi.DkError):
         capi.moe_grouped_gemm_fp8(xq.cuda()[:, :64].contiguous(), xs.cuda(), c["w13q"].cuda(), c["w13s"].cuda(),
                                   offs.cuda(), True)      # K % 128 != 0
+
+
+def test_tk_kernel_moe_layer_single_gpu(orc):
+    """The whole MoE layer through the Python entry points of tk_kernel on one GPU."""
+    import iris_py
+    import tk_kernel
+    T, H, F, E, k = 384, 256, 256, 8, 2
+    x, logits, w13q, w13s, w2q, w2s = orc.make_moe_inputs(T, H, F, E, k, seed=8)
+    idx_c, w_c = orc.moe_route(logits, k)
+    rop_c, por_c, offs_c, _ = orc.moe_permute(idx_c, E)
+    xq_c, xs_c = orc.quant_block128(orc.moe_gather_rows(x, por_c, k))
+    y_c, _, _ = orc.moe_ffn_ref(xq_c, xs_c, w13q, w13s, w2q, w2s, offs_c)
+    want = orc.moe_combine_ref(y_c, rop_c, w_c)
+
+    iris = iris_py.Iris(heap_size_mb=64)
+    view = iris.get_device_view()
+    idx, w = tk_kernel.moe_route(logits.cuda(), k)
+    rop, por, offs, counts = tk_kernel.moe_permute(idx, E)
+    assert torch.equal(idx.cpu(), idx_c) and torch.equal(rop.cpu(), rop_c) and torch.equal(offs.cpu(), offs_c)
+    R = int(offs_c[-1])
+    assert torch.equal(por.cpu()[:R], por_c)
+    xq, xs = tk_kernel.moe_quant(x.cuda(), por, 1, k)
+    assert torch.equal(xq.cpu()[:R], xq_c) and torch.equal(xs.cpu()[:R // 128], xs_c)
+    y = tk_kernel.moe_ffn_fp8(xq, xs, w13q.cuda(), w13s.cuda(), w2q.cuda(), w2s.cuda(), offs)
+    out = tk_kernel.moe_combine(y, idx, rop, w, E, view)
+    torch.cuda.synchronize()
+    assert tk_kernel.device_status()[0] == 0
+    assert orc.rel_fro(out.float().cpu(), want) <= TOL
