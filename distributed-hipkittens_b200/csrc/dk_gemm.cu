@@ -72,6 +72,7 @@ struct GemmArgs {
     const unsigned* red_flags;     // local flags [tiles_per_shard][world]
     unsigned* status;
     unsigned long long peer_wait_ns;
+    long long* dbg;  // [gridDim.x][DBG_SLOTS] stall counters, or null
 };
 
 enum : unsigned {
@@ -119,6 +120,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
     const WaitCtx wc{g.status, abort_sm, g.peer_wait_ns};
     const int num_tiles = g.tiles_m * g.tiles_n;
     const bool do_gemm = (g.phases & 1) != 0;
+    const long long dbg_t0 = clock64();
 
     if (threadIdx.x == 0) {
         *abort_sm = 0;
@@ -180,15 +182,20 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                 int acc = 0;
                 uint32_t acc_ph = 0;
                 bool ok = true;
+                long long dbg_mma_tmem = 0, dbg_mma_full = 0;
                 for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                    long long c0 = clock64();
                     if (!mbar_wait(bar_tempty + 8 * acc, acc_ph ^ 1, wc, SITE_TMEM_EMPTY, t)) break;
+                    dbg_mma_tmem += clock64() - c0;
                     tc_fence_after();
                     const uint32_t d_tmem = tmem_base + acc * BN;
                     for (int kb = 0; kb < g.num_kb; ++kb) {
+                        c0 = clock64();
                         if (!mbar_wait(bar_full + 8 * s, ph, wc, SITE_FULL, t)) {
                             ok = false;
                             break;
                         }
+                        dbg_mma_full += clock64() - c0;
                         tc_fence_after();
                         const uint32_t sa = ring + s * STAGE_BYTES;
                         const uint64_t da = umma_desc_sw128(sa);
@@ -210,6 +217,10 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                     acc ^= 1;
                     if (acc == 0) acc_ph ^= 1;
                 }
+                if (g.dbg != nullptr) {
+                    g.dbg[blockIdx.x * DBG_SLOTS + DBG_MMA_WAIT_TMEM] = dbg_mma_tmem;
+                    g.dbg[blockIdx.x * DBG_SLOTS + DBG_MMA_WAIT_FULL] = dbg_mma_full;
+                }
             }
         } else if (warp < 6) {
             // ------------------------------------------------ epilogue (warps 2..5)
@@ -219,15 +230,18 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
             int acc = 0;
             uint32_t acc_ph = 0;
             uint32_t epi_ph = 0;
+            long long dbg_acc = 0, dbg_smem = 0, dbg_landed = 0;
             for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
                 int m, n;
                 tile_coords(t, g, m, n);
                 const int owner = (m * BM) / g.rows_per_rank;
                 const int row0 = m * BM - owner * g.rows_per_rank + q * 32;  // row inside dst
                 // the whole warp takes the same branch: tcgen05.ld below is warp-collective
+                long long c0 = clock64();
                 if (!__all_sync(0xffffffffu,
                                 mbar_wait(bar_tfull + 8 * acc, acc_ph, wc, SITE_TMEM_FULL, t)))
                     break;
+                dbg_acc += clock64() - c0;
                 tc_fence_after();
                 const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
 #pragma unroll 1
@@ -247,8 +261,10 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                     if (g.epi_mode == 1) {
                         const uint32_t buf = my_epi + (c & 1) * EPI_BUF_BYTES;
                         // the store issued two chunks ago has finished reading this buffer
+                        c0 = clock64();
                         if (lane == 0) tma_store_wait_read<1>();
                         __syncwarp();
+                        dbg_smem += clock64() - c0;
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             const uint32_t addr = buf + lane * 128 + ((j ^ (lane & 7)) << 4);
@@ -284,6 +300,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
 
                 if (g.world > 1) {
                     // all four warps' stores must have landed before the owner is told
+                    c0 = clock64();
                     if (g.epi_mode == 1) {
                         if (lane == 0) tma_store_wait_all<0>();
                     }
@@ -308,10 +325,16 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                         }
                         if (!__all_sync(0xffffffffu, landed)) break;
                     }
+                    dbg_landed += clock64() - c0;
                     epi_ph ^= 1;
                 }
             }
             if (g.epi_mode == 1 && lane == 0) tma_store_wait_all<0>();
+            if (g.dbg != nullptr && ew == 0 && lane == 0) {
+                g.dbg[blockIdx.x * DBG_SLOTS + DBG_EPI_WAIT_ACC] = dbg_acc;
+                g.dbg[blockIdx.x * DBG_SLOTS + DBG_EPI_WAIT_SMEM] = dbg_smem;
+                g.dbg[blockIdx.x * DBG_SLOTS + DBG_EPI_WAIT_LANDED] = dbg_landed;
+            }
         }
     }
 
@@ -322,10 +345,12 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
     if (warp >= 6 && (g.phases & 2) != 0 && g.world > 1) {
         const int rt = threadIdx.x - (GEMM_THREADS - RED_THREADS);
         const size_t slot_elems = static_cast<size_t>(g.rows_per_rank) * g.N;
+        long long dbg_flag = 0, dbg_work = 0;
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
             int m, n;
             tile_coords(t, g, m, n);
             if ((m * BM) / g.rows_per_rank != g.rank) continue;
+            long long c0 = clock64();
             const int tm = (m * BM - g.rank * g.rows_per_rank) / BM;
             const int rtile = tm * g.tiles_n + n;
             if (rt < g.world)
@@ -333,6 +358,8 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                                SITE_RS_FLAG, rtile);
             named_bar_sync(2, RED_THREADS);
             if (*abort_sm) break;
+            dbg_flag += clock64() - c0;
+            c0 = clock64();
             // 128 rows x 32 16-byte vectors; 4 vectors per thread in flight per slot
 #pragma unroll 1
             for (int i0 = 0; i0 < BM * (BN / 8) / RED_THREADS; i0 += 4) {
@@ -376,11 +403,17 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                     *reinterpret_cast<uint4*>(g.red_out + off[u]) = o;
                 }
             }
+            dbg_work += clock64() - c0;
+        }
+        if (g.dbg != nullptr && rt == 0) {
+            g.dbg[blockIdx.x * DBG_SLOTS + DBG_RED_WAIT_FLAG] = dbg_flag;
+            g.dbg[blockIdx.x * DBG_SLOTS + DBG_RED_WORK] = dbg_work;
         }
     }
 
     tc_fence_before();
     __syncthreads();
+    if (g.dbg != nullptr && threadIdx.x == 0) g.dbg[blockIdx.x * DBG_SLOTS + DBG_TOTAL] = clock64() - dbg_t0;
     if (warp == 1 && do_gemm) {
         __syncwarp();
         tc_fence_after();
@@ -396,6 +429,9 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
 
 // --------------------------------------------------------------------------------------------
 // host side
+
+// Stall-counter buffer handed to every GEMM launch (null = off); see dk_gemm_debug_counters.
+static long long* g_gemm_dbg = nullptr;
 
 static int check_gemm_args(const void* A, const void* Bt, void* C, int M, int N, int K) {
     DK_REQUIRE(A != nullptr && Bt != nullptr && C != nullptr, "null operand");
@@ -449,6 +485,7 @@ int gemm_bf16_impl(const void* A, const void* Bt, void* C, int M, int N, int K, 
     rc = device_status_ptr(&g.status);
     if (rc != DK_OK) return rc;
     g.peer_wait_ns = peer_wait_ns();
+    g.dbg = g_gemm_dbg;
     int sms = 0;
     rc = sm_count(&sms);
     if (rc != DK_OK) return rc;
@@ -510,7 +547,10 @@ int gemm_rs_impl(const void* A, const void* Bt, void* out, int M, int N, int Klo
     g.rank = rank;
     g.rows_per_rank = mloc;
     g.m_tile_rot = ((rank + 1) % world) * (mloc / BM);
-    g.epi_mode = epilogue < 0 ? 1 : epilogue;
+    // Pushes to peers always use TMA bulk stores: with direct 16-byte stores to peer memory an
+    // 8-GPU run stalled until its peer waits ran out, so that variant is not offered across GPUs.
+    (void)epilogue;
+    g.epi_mode = 1;
     g.phases = phases;
     g.epoch = seq;
     char* ws_local = static_cast<char*>(workspace);
@@ -530,6 +570,7 @@ int gemm_rs_impl(const void* A, const void* Bt, void* out, int M, int N, int Klo
     rc = device_status_ptr(&g.status);
     if (rc != DK_OK) return rc;
     g.peer_wait_ns = peer_wait_ns();
+    g.dbg = g_gemm_dbg;
     int sms = 0;
     rc = sm_count(&sms);
     if (rc != DK_OK) return rc;
@@ -538,6 +579,11 @@ int gemm_rs_impl(const void* A, const void* Bt, void* out, int M, int N, int Klo
 }
 
 }  // namespace dk
+
+extern "C" int dk_gemm_debug_counters(long long* device_buffer) {
+    dk::g_gemm_dbg = device_buffer;
+    return DK_OK;
+}
 
 extern "C" size_t dk_gemm_rs_workspace_bytes(int M, int N, int world) {
     if (M <= 0 || N <= 0 || world < 1 || world > DK_MAX_RANKS || M % world != 0) return 0;

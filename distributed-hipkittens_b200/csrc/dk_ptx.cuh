@@ -79,6 +79,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Error record written by the first wait that gives up: {code, block, site, detail}.
+// Optional per-CTA stall accounting (clock64 ticks), enabled by handing the kernel a buffer.
+enum : int { DBG_MMA_WAIT_TMEM = 0, DBG_MMA_WAIT_FULL, DBG_EPI_WAIT_ACC, DBG_EPI_WAIT_SMEM,
+             DBG_EPI_WAIT_LANDED, DBG_RED_WAIT_FLAG, DBG_RED_WORK, DBG_TOTAL, DBG_SLOTS };
+
 struct WaitCtx {
     unsigned* status;        // 4 words in host-mapped memory (may be null)
     volatile int* abort_sm;  // CTA-wide abort flag in shared memory
@@ -347,6 +351,13 @@ __device__ __forceinline__ bool signal_wait_ge(const unsigned* p, unsigned targe
     while (static_cast<int>(signal_load_acquire_sys(p) - target) < 0) {
         if ((++spins & 0x3f) == 0) {
             if (*w.abort_sm) return false;
+            // An error record the host has not read yet means an earlier wait already ran out
+            // (here or in an earlier launch): the job is broken, so do not wait the limit again.
+            if ((spins & 0x3fff) == 0 && w.status != nullptr &&
+                *reinterpret_cast<volatile unsigned*>(w.status) != 0u) {
+                *w.abort_sm = 1;
+                return false;
+            }
             if (globaltimer_ns() - t0 > w.peer_limit_ns) {
                 record_timeout(w, DK_DEV_PEER_TIMEOUT, site, detail);
                 return false;

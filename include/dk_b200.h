@@ -146,6 +146,15 @@ int dk_gemm_rs(const void* A, const void* Bt, void* out, int M, int N, int Kloc,
 int dk_gemm_rs_phase(const void* A, const void* Bt, void* out, int M, int N, int Kloc,
                      void* workspace, const dk_view* view, unsigned seq, int phases, int epilogue,
                      void* stream);
+/* (`epilogue` is honoured for world == 1 only: pushes to peers always use TMA bulk stores.) */
+
+/*
+ * Stall accounting for the GEMM kernels, for tuning. device_buffer holds 8 int64 per CTA (148 CTAs
+ * at most): clock ticks the MMA warp waited for a free accumulator / for operands, the epilogue
+ * waited for an accumulator / for its staging buffer / for its stores to land, the reducers waited
+ * for flags / spent summing, and the CTA's total. NULL switches it off (the default).
+ */
+int dk_gemm_debug_counters(long long* device_buffer);
 
 /* ------------------------------------------------------------------ all-reduce */
 /*
