@@ -21,10 +21,11 @@
 //
 // Reduce-scatter mode (world > 1): A and Bt hold this rank's K-shard. Each finished 128x256 tile
 // of the partial product is written, as bf16, into slot [rank] of the staging area of the rank
-// that OWNS those rows (peer memory, over NVLink), followed by a release store of the call's
-// epoch into that tile's flag [rank] at the owner. Row-tiles are visited starting with the rows
+// that OWNS those rows (peer memory, over NVLink) as sixteen contiguous 4 KiB bulk copies (the
+// staging area is tile-major, so a peer write never has to be scattered over rows), followed by
+// a release store of the call number into that tile's flag [rank] at the owner. Row-tiles are visited starting with the rows
 // of rank+1 and ending with this rank's own, so every link is busy from the first tile on.
-//   warps 6-9   reducers: for every tile of this rank's own rows that this CTA computes, wait
+//   warps 6-11  reducers: for every tile of this rank's own rows that this CTA computes, wait
 //               (bounded) for the `world` flags, sum the `world` bf16 partials in fp32 in rank order
 //               and write bf16, while the MMA warp is already working on the next tile.
 #include "dk_heap.h"
@@ -45,8 +46,8 @@ constexpr int EPI_BUF_BYTES = 32 * 128;  // 32 rows x 64 bf16 per epilogue warp
 constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;
 constexpr int CTRL_BYTES = 256;
 constexpr int GEMM_SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + CTRL_BYTES;
-constexpr int GEMM_THREADS = 320;  // TMA, MMA, 4 epilogue warps, 4 reducer warps
-constexpr int RED_THREADS = 128;
+constexpr int GEMM_THREADS = 384;  // TMA, MMA, 4 epilogue warps, 6 reducer warps
+constexpr int RED_THREADS = 192;
 constexpr int GROUP_M = 16;
 constexpr int TMEM_COLS = 512;
 
@@ -96,6 +97,85 @@ __device__ __forceinline__ void tile_coords(int t, const GemmArgs& g, int& m, in
     if (m >= g.tiles_m) m -= g.tiles_m;
 }
 
+// Epilogue warps call this once the bulk stores of a tile have completed (each warp's issuing lane
+// has waited on its own store groups): meet on the CTA's mbarrier (release/acquire at CTA scope),
+// then one thread release-stores the call number into the tile's flag at the owner at system
+// scope; by cumulativity that release covers the completed stores of all four warps.
+// Returns false if the bounded wait gave up.
+__device__ __forceinline__ bool epi_signal(const GemmArgs& g, const WaitCtx& wc, uint32_t bar_epi,
+                                           uint32_t epi_ph, int ew, int lane, int owner,
+                                           int tile_in_shard) {
+    if (lane == 0) mbar_arrive(bar_epi);
+    if (ew != 0) return true;
+    bool landed = true;
+    if (lane == 0) {
+        landed = mbar_wait(bar_epi, epi_ph, wc, SITE_EPI_DONE, tile_in_shard);
+        if (landed)
+            signal_store_release_sys(
+                g.flag_dst[owner] + static_cast<size_t>(tile_in_shard) * g.world + g.rank, g.epoch);
+    }
+    return __all_sync(0xffffffffu, landed);
+}
+
+// Sum `world` staged partial tiles into bf16 rows of the output. A staged tile is the 64 KiB image
+// the epilogue wrote: block (q, c) of 4 KiB holds rows q*32.. x columns c*64.. as 32 rows of 128
+// bytes whose 16-byte chunks are XOR-swizzled by (row & 7). UNR vectors per thread in flight per slot.
+template <int UNR, int W>
+__device__ __forceinline__ void reduce_tile(const __nv_bfloat16* __restrict__ src,
+                                            __nv_bfloat16* __restrict__ dst, int N, int world, int rt,
+                                            int tm, int n, int rtile, size_t slot_elems) {
+    constexpr int TILE_VECS = BM * (BN / 8);
+    const uint4* tsrc = reinterpret_cast<const uint4*>(src + static_cast<size_t>(rtile) * (BM * BN));
+    __nv_bfloat16* tdst = dst + static_cast<size_t>(tm) * BM * N + n * BN;
+    const size_t slot_vecs = slot_elems / 8;
+#pragma unroll 1
+    for (int base = rt; base < TILE_VECS; base += RED_THREADS * UNR) {
+        uint4 v[UNR][W];
+        int off[UNR];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            const int vi = base + u * RED_THREADS;
+            const int blk = vi >> 8;             // 256 vectors per 4 KiB block
+            const int row_in = (vi >> 3) & 31;
+            const int j = (vi & 7) ^ (row_in & 7);
+            const int row = (blk >> 2) * 32 + row_in;
+            const int col = (blk & 3) * 64 + j * 8;
+            off[u] = (vi < TILE_VECS && n * BN + col + 8 <= N) ? row * N + col : -1;
+#pragma unroll
+            for (int s = 0; s < W; ++s)
+                if (s < world && off[u] >= 0)
+                    // L2 read: the partials were written by peers while this kernel ran
+                    v[u][s] = __ldcg(tsrc + s * slot_vecs + vi);
+        }
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            if (off[u] < 0) continue;
+            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+            for (int s = 0; s < W; ++s) {
+                if (s < world) {
+                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[u][s]);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = __bfloat1622float2(h[i]);
+                        acc[2 * i] += f.x;
+                        acc[2 * i + 1] += f.y;
+                    }
+                }
+            }
+            uint4 o;
+            o.x = pack_bf16x2(acc[0], acc[1]);
+            o.y = pack_bf16x2(acc[2], acc[3]);
+            o.z = pack_bf16x2(acc[4], acc[5]);
+            o.w = pack_bf16x2(acc[6], acc[7]);
+            *reinterpret_cast<uint4*>(tdst + off[u]) = o;
+        }
+    }
+}
+
+// W = upper bound of g.world this instantiation serves (2, 4 or 8); it only sizes the reducers'
+// register arrays.
+template <int W>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
     extern __shared__ uint8_t smem_raw[];
@@ -230,7 +310,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
             int acc = 0;
             uint32_t acc_ph = 0;
             uint32_t epi_ph = 0;
-            long long dbg_acc = 0, dbg_smem = 0, dbg_landed = 0;
+            long long dbg_acc = 0, dbg_smem = 0, dbg_landed = 0, dbg_signal = 0, dbg_drain = 0;
             for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
                 int m, n;
                 tile_coords(t, g, m, n);
@@ -242,6 +322,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                                 mbar_wait(bar_tfull + 8 * acc, acc_ph, wc, SITE_TMEM_FULL, t)))
                     break;
                 dbg_acc += clock64() - c0;
+                const long long c_drain = clock64();
                 tc_fence_after();
                 const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
 #pragma unroll 1
@@ -276,7 +357,17 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                         fence_proxy_async_smem();
                         __syncwarp();
                         if (lane == 0) {
-                            tma_store_2d(&maps.out[owner], buf, col0, row0);
+                            if (g.world > 1) {
+                                // staging is tile-major: the tile's 64 KiB image is 16 blocks of
+                                // 4 KiB (lane quarter q, column chunk c), each an exact copy of
+                                // this swizzled buffer, so the peer sees one contiguous 4 KiB write
+                                const int tis = ((m * BM - owner * g.rows_per_rank) / BM) * g.tiles_n + n;
+                                bulk_store_1d(g.dst[owner] + static_cast<size_t>(tis) * (BM * BN) +
+                                                  (q * (BN / 64) + c) * (EPI_BUF_BYTES / 2),
+                                              buf, EPI_BUF_BYTES);
+                            } else {
+                                tma_store_2d(&maps.out[owner], buf, col0, row0);
+                            }
                             tma_store_commit();
                         }
                     } else {
@@ -299,33 +390,19 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                 if (acc == 0) acc_ph ^= 1;
 
                 if (g.world > 1) {
-                    // all four warps' stores must have landed before the owner is told
+                    // Tell the owner once all four warps' stores of this tile have landed. The
+                    // bulk stores complete through wait_group, the warps meet on an mbarrier, and
+                    // ONE system-scope release store publishes the flag: no other fence is issued
+                    // (system-scope fences next to NVLink traffic cost tens of microseconds each).
+                    dbg_drain += clock64() - c_drain;
                     c0 = clock64();
-                    if (g.epi_mode == 1) {
-                        if (lane == 0) tma_store_wait_all<0>();
-                    }
+                    if (lane == 0) tma_store_wait_all<0>();
                     __syncwarp();
-                    if (lane == 0) {
-                        __threadfence_system();
-                        mbar_arrive(bar_epi);
-                    }
-                    if (ew == 0) {
-                        bool landed = true;
-                        if (lane == 0) {
-                            landed = mbar_wait(bar_epi, epi_ph, wc, SITE_EPI_DONE, t);
-                            if (landed) {
-                                const int tile_in_shard =
-                                    ((m * BM - owner * g.rows_per_rank) / BM) * g.tiles_n + n;
-                                __threadfence_system();
-                                signal_store_release_sys(g.flag_dst[owner] +
-                                                             static_cast<size_t>(tile_in_shard) * g.world +
-                                                             g.rank,
-                                                         g.epoch);
-                            }
-                        }
-                        if (!__all_sync(0xffffffffu, landed)) break;
-                    }
                     dbg_landed += clock64() - c0;
+                    c0 = clock64();
+                    const int tis = ((m * BM - owner * g.rows_per_rank) / BM) * g.tiles_n + n;
+                    if (!epi_signal(g, wc, bar_epi, epi_ph, ew, lane, owner, tis)) break;
+                    dbg_signal += clock64() - c0;
                     epi_ph ^= 1;
                 }
             }
@@ -334,17 +411,23 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                 g.dbg[blockIdx.x * DBG_SLOTS + DBG_EPI_WAIT_ACC] = dbg_acc;
                 g.dbg[blockIdx.x * DBG_SLOTS + DBG_EPI_WAIT_SMEM] = dbg_smem;
                 g.dbg[blockIdx.x * DBG_SLOTS + DBG_EPI_WAIT_LANDED] = dbg_landed;
+                if ((g.phases & 2) == 0) {
+                    // produce-only launches have no reducers: their two slots carry the time spent
+                    // draining accumulators and the time spent in fences + flag stores instead
+                    g.dbg[blockIdx.x * DBG_SLOTS + DBG_RED_WAIT_FLAG] = dbg_drain;
+                    g.dbg[blockIdx.x * DBG_SLOTS + DBG_RED_WORK] = dbg_signal;
+                }
             }
         }
     }
 
-    // -------------------------------------------------------- reducers (warps 6..9, world > 1)
+    // -------------------------------------------------------- reducers (warps 6..11, world > 1)
     // They walk the same tile list as the GEMM roles and pick the tiles whose rows this rank owns:
     // the CTA that computes this rank's own partial of a tile (the last contribution to arrive,
     // by the visiting order) also sums that tile, while the MMA warp is already on the next one.
     if (warp >= 6 && (g.phases & 2) != 0 && g.world > 1) {
         const int rt = threadIdx.x - (GEMM_THREADS - RED_THREADS);
-        const size_t slot_elems = static_cast<size_t>(g.rows_per_rank) * g.N;
+        const size_t slot_elems = static_cast<size_t>(g.rows_per_rank) * g.tiles_n * BN;
         long long dbg_flag = 0, dbg_work = 0;
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
             int m, n;
@@ -360,49 +443,8 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
             if (*abort_sm) break;
             dbg_flag += clock64() - c0;
             c0 = clock64();
-            // 128 rows x 32 16-byte vectors; 4 vectors per thread in flight per slot
-#pragma unroll 1
-            for (int i0 = 0; i0 < BM * (BN / 8) / RED_THREADS; i0 += 4) {
-                uint4 v[4][DK_MAX_RANKS];
-                size_t off[4];
-                bool ok[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int vi = rt + (i0 + u) * RED_THREADS;
-                    const int r = tm * BM + vi / (BN / 8);
-                    const int cidx = n * BN + (vi % (BN / 8)) * 8;
-                    ok[u] = cidx + 8 <= g.N;
-                    off[u] = static_cast<size_t>(r) * g.N + cidx;
-#pragma unroll
-                    for (int s = 0; s < DK_MAX_RANKS; ++s)
-                        if (s < g.world && ok[u])
-                            // L2 read: the partials were written by peers while this kernel ran
-                            v[u][s] = __ldcg(reinterpret_cast<const uint4*>(g.red_src + s * slot_elems + off[u]));
-                }
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    if (!ok[u]) continue;
-                    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-                    for (int s = 0; s < DK_MAX_RANKS; ++s) {
-                        if (s < g.world) {
-                            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[u][s]);
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const float2 f = __bfloat1622float2(h[i]);
-                                acc[2 * i] += f.x;
-                                acc[2 * i + 1] += f.y;
-                            }
-                        }
-                    }
-                    uint4 o;
-                    o.x = pack_bf16x2(acc[0], acc[1]);
-                    o.y = pack_bf16x2(acc[2], acc[3]);
-                    o.z = pack_bf16x2(acc[4], acc[5]);
-                    o.w = pack_bf16x2(acc[6], acc[7]);
-                    *reinterpret_cast<uint4*>(g.red_out + off[u]) = o;
-                }
-            }
+            // 128 rows x 32 16-byte vectors; world * UNR = 16 vectors per thread in flight
+            reduce_tile<16 / W, W>(g.red_src, g.red_out, g.N, g.world, rt, tm, n, rtile, slot_elems);
             dbg_work += clock64() - c0;
         }
         if (g.dbg != nullptr && rt == 0) {
@@ -441,18 +483,25 @@ static int check_gemm_args(const void* A, const void* Bt, void* C, int M, int N,
     return DK_OK;
 }
 
-static int launch_gemm(const GemmMaps& maps, const GemmArgs& args, int grid, cudaStream_t stream) {
+template <int W>
+static int launch_gemm_w(const GemmMaps& maps, const GemmArgs& args, int grid, cudaStream_t stream) {
     static bool attr_set[64] = {false};
     int dev = 0;
     DK_CUDA_OK(cudaGetDevice(&dev));
     if (!attr_set[dev & 63]) {
-        DK_CUDA_OK(cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        DK_CUDA_OK(cudaFuncSetAttribute(gemm_bf16_kernel<W>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         GEMM_SMEM_BYTES));
         attr_set[dev & 63] = true;
     }
-    gemm_bf16_kernel<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(maps, args);
+    gemm_bf16_kernel<W><<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(maps, args);
     DK_CUDA_OK(cudaGetLastError());
     return DK_OK;
+}
+
+static int launch_gemm(const GemmMaps& maps, const GemmArgs& args, int grid, cudaStream_t stream) {
+    if (args.world <= 2) return launch_gemm_w<2>(maps, args, grid, stream);
+    if (args.world <= 4) return launch_gemm_w<4>(maps, args, grid, stream);
+    return launch_gemm_w<8>(maps, args, grid, stream);
 }
 
 int gemm_bf16_impl(const void* A, const void* Bt, void* C, int M, int N, int K, int epilogue,
@@ -495,10 +544,11 @@ int gemm_bf16_impl(const void* A, const void* Bt, void* C, int M, int N, int K, 
 
 // ---- reduce-scatter ---------------------------------------------------------------------------
 // Workspace layout (identical offset on every rank, inside the symmetric heap):
-//   stage [2 parities][world slots][rows_per_rank][N] bf16, then
+//   stage [2 parities][world slots][tiles of the shard][64 KiB tile image] bf16, then
 //   flags [2 parities][tiles per shard][world] u32 (offset rounded up to 256 bytes)
 static size_t rs_stage_bytes(int M, int N, int world) {
-    return static_cast<size_t>(2) * world * (M / world) * N * 2;
+    const size_t n_padded = static_cast<size_t>((N + BN - 1) / BN) * BN;  // whole 128 x 256 tiles
+    return static_cast<size_t>(2) * world * (M / world) * n_padded * 2;
 }
 static size_t rs_flag_words(int M, int N, int world) {
     const int shard_tiles = ((M / world) / BM) * ((N + BN - 1) / BN);
@@ -528,7 +578,7 @@ int gemm_rs_impl(const void* A, const void* Bt, void* out, int M, int N, int Klo
     DK_REQUIRE(seq != 0, "sequence numbers start at 1");
     const int rank = view->rank;
     const int mloc = M / world;
-    const size_t slot_elems = static_cast<size_t>(mloc) * N;
+    const size_t slot_elems = static_cast<size_t>(mloc) * ((N + BN - 1) / BN) * BN;
     const unsigned parity = seq & 1u;
 
     GemmMaps maps;
@@ -560,10 +610,9 @@ int gemm_rs_impl(const void* A, const void* Bt, void* out, int M, int N, int Klo
         char* ws_o = static_cast<char*>(peer_ptr(view, ws_local, o));
         g.dst[o] = reinterpret_cast<__nv_bfloat16*>(ws_o + stage_par) + static_cast<size_t>(rank) * slot_elems;
         g.flag_dst[o] = reinterpret_cast<unsigned*>(ws_o + flags_off);
-        rc = make_tmap_2d(&maps.out[o], g.dst[o], 2, N, mloc, static_cast<uint64_t>(N) * 2, 64, 32);
-        if (rc != DK_OK) return rc;
     }
-    for (int o = world; o < DK_MAX_RANKS; ++o) maps.out[o] = maps.out[0];
+    // the output maps are used by the plain GEMM only; fill them with a valid descriptor
+    for (int o = 0; o < DK_MAX_RANKS; ++o) maps.out[o] = maps.a;
     g.red_src = reinterpret_cast<const __nv_bfloat16*>(ws_local + stage_par);
     g.red_out = static_cast<__nv_bfloat16*>(out);
     g.red_flags = reinterpret_cast<const unsigned*>(ws_local + flags_off);
