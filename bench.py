@@ -1,18 +1,22 @@
 #!/usr/bin/env python
-"""Benchmark of the hot path: row-parallel bf16 GEMM fused with reduce-scatter.
+"""Benchmark of the hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload ...]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload gemm_rs|allreduce|moe_mixtral|moe_dsv3]
 
-One process per GPU (under torchrun for N > 1). A step is one pass of the operator over one set
-of synthetic inputs: tokens M=8192, K=28672 split K/N across the N ranks, N=8192 outputs
-(the Llama-70B MLP down-projection shape), output reduce-scattered along M. Total work is fixed
-as N grows (strong scaling); at N=1 the operator is the plain GEMM.
+One process per GPU (under torchrun for N > 1). The default workload, the one the headline metric
+is quoted on, is the row-parallel bf16 GEMM fused with reduce-scatter: tokens M=8192, K=28672 split
+K/N across the N ranks, N=8192 outputs (the Llama-70B MLP down-projection shape), output
+reduce-scattered along M. Total work is fixed as N grows (strong scaling); at N=1 the operator is
+the plain GEMM. The other workloads measure the remaining operators of the path on the shapes
+BASELINE.json names (TP all-reduce of 1 MiB / 128 MiB; Mixtral- and DeepSeek-V3-shaped fp8 MoE
+layers, expert-parallel when N > 1).
 
-Prints ONE JSON line (rank 0). `value` is whole-job TFLOP/s with inputs resident in HBM, timed
-with CUDA events, max over ranks. `e2e` is the same metric through the Python entry point
-(tk_kernel.gemm_rs) with pinned HOST operands copied in and the result copied out every step.
-`cpu_baseline` / `--impl reference` time the reference's torch CPU path
-(torch.matmul on the host, distributed-kernels/bf16_gemm/example.py:105) on a bounded sample.
+Prints ONE JSON line (rank 0). `value` is whole-job throughput with inputs resident in HBM, timed
+with CUDA events, max over ranks. `e2e` is the same metric through the Python entry points with
+pinned HOST operands copied in and the result copied out every step. `cpu_baseline` /
+`--impl reference` time the reference's torch CPU path (torch.matmul on the host,
+distributed-kernels/bf16_gemm/example.py:105) on a bounded sample.
 """
 from __future__ import annotations
 
@@ -32,17 +36,27 @@ sys.path.insert(0, str(ROOT / "distributed-hipkittens_b200"))
 
 M_TOK, K_FULL, N_OUT = 8192, 28672, 8192
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+NVLINK_GBS = 770.0   # measured peer copy per direction on this pool (nominal 900)
 
 
 def load_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         try:
-            d = json.loads(p.read_text())
-            return d, "measured"
+            return json.loads(p.read_text()), "measured"
         except Exception:
             pass
     return dict(FALLBACK_PEAKS), "fallback"
+
+
+def load_traffic(key):
+    prof = ROOT / "profiles" / "traffic.json"
+    if prof.exists():
+        try:
+            return json.loads(prof.read_text()).get(key)
+        except Exception:
+            return None
+    return None
 
 
 class ClockSampler:
@@ -106,9 +120,9 @@ class ClockSampler:
 
 
 def cpu_reference_tflops(budget_s: float = 15.0):
-    """The reference's torch CPU path on a bounded sample of the workload: the first `rows` token
-    rows against the full [N, K] weight, torch.matmul of the bf16-rounded operands in fp32 with all
-    host threads. Returns (TFLOP/s, threads, description, seconds)."""
+    """The reference's torch CPU path on a bounded sample of the GEMM workload: the first `rows`
+    token rows against the full [N, K] weight, torch.matmul of the bf16-rounded operands in fp32
+    with all host threads. Returns (TFLOP/s, threads, description, seconds)."""
     import torch
     from oracle import dk_oracle as orc
     threads = torch.get_num_threads()
@@ -128,14 +142,14 @@ def cpu_reference_tflops(budget_s: float = 15.0):
     orc.gemm_ref(A, Bt)
     dt = time.perf_counter() - t0
     tf = 2.0 * rows * N_OUT * K_FULL / dt / 1e12
-    return tf, threads, f"first {rows} of {M_TOK} token rows x full N={N_OUT}, K={K_FULL} (oracle gemm_ref, torch CPU fp32)", dt
+    return tf, threads, (f"first {rows} of {M_TOK} token rows x full N={N_OUT}, K={K_FULL} "
+                         f"(oracle gemm_ref, torch CPU fp32)"), dt
 
 
 def run_reference(args, rank):
     """--impl reference: the reference's CPU implementation of the path, rank 0 only."""
     if rank != 0:
         return
-    import torch
     vals = []
     desc, threads = "", 1
     for i in range(args.warmup + args.steps):
@@ -157,16 +171,338 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------------------------ workloads
+class GemmRs:
+    """Row-parallel GEMM + reduce-scatter (the headline workload)."""
+    metric, unit, dtype, scaling = "gemm_rs_tflops", "TFLOP/s", "bf16", "strong"
+    launches_per_step = 1
+
+    def __init__(self, ctx):
+        import torch
+        self.ctx = ctx
+        P, rank = ctx.world, ctx.rank
+        assert K_FULL % P == 0 and M_TOK % (P * 128) == 0
+        self.Kloc, self.Mloc = K_FULL // P, M_TOK // P
+        ws_mb = (2 * M_TOK * ((N_OUT + 255) // 256 * 256) * 2) // (1 << 20) + 64 if P > 1 else 0
+        ctx.make_heap(ws_mb + self.Mloc * N_OUT * 2 * 2 // (1 << 20) + 64)
+        self.shard_bytes = (M_TOK + N_OUT) * self.Kloc * 2
+        self.nsets = max(2, math.ceil(256e6 / self.shard_bytes))
+        g = torch.Generator(device="cuda").manual_seed(1000 + rank)
+        self.sets = []
+        for _ in range(self.nsets):
+            A = torch.randn(M_TOK, self.Kloc, device="cuda", generator=g).to(torch.bfloat16)
+            Bt = (torch.randn(N_OUT, self.Kloc, device="cuda", generator=g) / math.sqrt(K_FULL)).to(torch.bfloat16)
+            self.sets.append((A, Bt))
+        self.out_t = ctx.iris.empty([self.Mloc, N_OUT], "bfloat16")
+        self.out = torch.as_tensor(self.out_t, device="cuda").view(torch.bfloat16)
+        self.work = 2.0 * M_TOK * N_OUT * K_FULL          # FLOP per step, whole job
+        self.scale = 1e12
+
+    def step(self, i):
+        A, Bt = self.sets[i % self.nsets]
+        self.ctx.tk.gemm_rs(A, Bt, self.out, self.ctx.view)
+
+    def e2e_setup(self):
+        import torch
+        A, Bt = self.sets[0]
+        self.hA = torch.empty(M_TOK, self.Kloc, dtype=torch.bfloat16).pin_memory()
+        self.hB = torch.empty(N_OUT, self.Kloc, dtype=torch.bfloat16).pin_memory()
+        self.hA.copy_(A)
+        self.hB.copy_(Bt)
+        self.hO = torch.empty(self.Mloc, N_OUT, dtype=torch.bfloat16).pin_memory()
+        self.dA, self.dB = torch.empty_like(A), torch.empty_like(Bt)
+        return (self.hA.numel() + self.hB.numel()) * 2, self.hO.numel() * 2
+
+    def e2e_step(self):
+        self.dA.copy_(self.hA, non_blocking=True)
+        self.dB.copy_(self.hB, non_blocking=True)
+        self.ctx.tk.gemm_rs(self.dA, self.dB, self.out, self.ctx.view)
+        self.hO.copy_(self.out, non_blocking=True)
+
+    def config(self, value):
+        P = self.ctx.world
+        return {"workload": f"gemm_rs M={M_TOK} N={N_OUT} K={K_FULL} K-sharded over {P} GPU(s), "
+                            f"out rows reduce-scattered (Llama-70B MLP down-proj shape)",
+                "l2": f"{self.nsets} operand sets of {self.shard_bytes / 1e6:.0f} MB rotated: "
+                      f"{(self.nsets - 1) * self.shard_bytes / 1e6:.0f} MB of other operands pass between two "
+                      f"uses of a set (L2 is 126 MB)",
+                "per_gpu_tflops": value / P}
+
+    def roofline(self, ms_step, sustained, peaks, peak_src):
+        P = self.ctx.world
+        peak = peaks.get("bf16_tflops_sustained" if sustained else "bf16_tflops")
+        achieved = (self.work / P) / (ms_step * 1e-3) / 1e12
+        r = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+             "frac": achieved / peak if peak else None, "traffic": load_traffic(f"gemm_rs_p{P}"),
+             "peak_source": f"{peak_src} ({'sustained' if sustained else 'burst'} cuBLAS bf16)"}
+        if P > 1:
+            egress = 2.0 * M_TOK * N_OUT * (P - 1) / P          # bf16 partials leaving this GPU
+            r["nvlink"] = {"egress_bytes_per_step": egress,
+                           "achieved_gbs": egress / (ms_step * 1e-3) / 1e9, "peak_gbs": NVLINK_GBS,
+                           "floor_ms": egress / (NVLINK_GBS * 1e9) * 1e3}
+        return r
+
+
+class AllReduce:
+    """TP all-reduce of bf16 activations: decode [64 x 8192] (1 MiB) and prefill [8192 x 8192]
+    (128 MiB); a step is one all-reduce of each."""
+    metric, unit, dtype, scaling = "allreduce_busbw", "GB/s", "bf16", "weak"
+    launches_per_step = 2
+
+    def __init__(self, ctx):
+        import torch
+        self.ctx = ctx
+        ctx.make_heap(3 * 129 + 3 * 2 + 64)
+        g = torch.Generator(device="cuda").manual_seed(100 + ctx.rank)
+        self.bufs = {}
+        for name, shape in (("decode", (64, 8192)), ("prefill", (8192, 8192))):
+            xs = []
+            for _ in range(2):      # two input buffers, alternated
+                t = torch.as_tensor(ctx.iris.empty(list(shape)), device="cuda").view(torch.bfloat16)
+                t.copy_(torch.randn(*shape, device="cuda", generator=g).to(torch.bfloat16))
+                xs.append(t)
+            o = torch.as_tensor(ctx.iris.empty(list(shape)), device="cuda").view(torch.bfloat16)
+            self.bufs[name] = (xs, o)
+        P = ctx.world
+        S = (64 * 8192 + 8192 * 8192) * 2
+        self.work = S * (2.0 * (P - 1) / P if P > 1 else 1.0)     # bus bytes per step
+        self.scale = 1e9
+        self.detail = {}
+
+    def step(self, i):
+        for name in ("decode", "prefill"):
+            xs, o = self.bufs[name]
+            self.ctx.tk.allreduce(xs[i % 2], o, self.ctx.view, -1)
+
+    def time_each(self):
+        """Separate timings of the two messages and of both algorithms (reported in config)."""
+        import torch
+        out = {}
+        for name in ("decode", "prefill"):
+            xs, o = self.bufs[name]
+            for algo, an in ((0, "oneshot"), (1, "twoshot")):
+                if self.ctx.world == 1 and algo == 1:
+                    continue
+                for _ in range(3):
+                    self.ctx.tk.allreduce(xs[0], o, self.ctx.view, algo)
+                self.ctx.barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                n = 20
+                e0.record()
+                for j in range(n):
+                    self.ctx.tk.allreduce(xs[j % 2], o, self.ctx.view, algo)
+                e1.record()
+                self.ctx.barrier()
+                out[f"{name}_{an}_us"] = self.ctx.max_over_ranks(e0.elapsed_time(e1) / n) * 1e3
+        self.detail = out
+
+    def e2e_setup(self):
+        return None
+
+    def config(self, value):
+        c = {"workload": f"TP all-reduce bf16, 1 MiB [64x8192] + 128 MiB [8192x8192] per step, "
+                         f"{self.ctx.world} GPU(s), algorithm picked by size",
+             "l2": "two input buffers alternated; the 128 MiB message exceeds L2"}
+        c.update(self.detail)
+        return c
+
+    def roofline(self, ms_step, sustained, peaks, peak_src):
+        ach = self.work / (ms_step * 1e-3) / 1e9
+        return {"bound": "nvlink", "achieved": ach, "peak": NVLINK_GBS, "unit": "GB/s",
+                "frac": ach / NVLINK_GBS, "traffic": None,
+                "peak_source": "measured peer copy per direction on this pool (770 GB/s)"}
+
+
+class Moe:
+    """fp8 block-scaled MoE layer: route -> permute -> (dispatch) -> quantise -> gate/up grouped
+    GEMM + SiLU*mul + requantise -> down grouped GEMM -> combine. Expert-parallel when N > 1."""
+    unit, dtype, scaling = "TFLOP/s", "fp8_e4m3", "strong"
+
+    SHAPES = {"moe_mixtral": dict(T=16384, H=4096, F=14336, E=8, k=2, zipf=0.0,
+                                  name="Mixtral-8x7B-shaped: 16384 tokens, hidden 4096, ffn 14336, E=8 top-2"),
+              "moe_dsv3": dict(T=32768, H=7168, F=2048, E=256, k=8, zipf=1.1,
+                               name="DeepSeek-V3-shaped: 32768 tokens, hidden 7168, expert inter 2048, "
+                                    "E=256 top-8, Zipf(1.1)")}
+
+    def __init__(self, ctx, which):
+        import torch
+        self.ctx = ctx
+        s = self.SHAPES[which]
+        self.metric = which + "_tflops"
+        self.s = s
+        P, rank = ctx.world, ctx.rank
+        T, H, F, E, k = s["T"], s["H"], s["F"], s["E"], s["k"]
+        assert E % P == 0 and T % P == 0
+        self.epr, self.Tl = E // P, T // P
+        capi = ctx.capi
+        self.cap = capi.lib().dk_moe_rows_capacity(T, k, self.epr, 128)
+        heap_mb = ((2 * self.cap * H * 2 + T * k * 4) // (1 << 20) if P > 1 else 0) + 64
+        ctx.make_heap(heap_mb)
+        g = torch.Generator(device="cuda").manual_seed(7 + rank)
+        self.x = torch.randn(self.Tl, H, device="cuda", generator=g).to(torch.bfloat16)
+        logits = torch.randn(self.Tl, E, device="cuda", generator=g)
+        if s["zipf"] > 0:
+            pi = torch.randperm(E, generator=torch.Generator().manual_seed(1)).float()
+            p = (pi + 1.0) ** (-s["zipf"])
+            logits = logits + torch.log(p / p.sum()).cuda()[None, :]
+        self.logits = logits.contiguous()
+        # this rank's experts, quantised with the library's own block quantiser
+        w13q, w13s, w2q, w2s = [], [], [], []
+        for _ in range(self.epr):
+            w = (torch.randn(2 * F, H, device="cuda", generator=g) / math.sqrt(H)).to(torch.bfloat16)
+            q, sc = capi.quant_block128(w)
+            w13q.append(q)
+            w13s.append(sc)
+            w = (torch.randn(H, F, device="cuda", generator=g) / math.sqrt(F)).to(torch.bfloat16)
+            q, sc = capi.quant_block128(w)
+            w2q.append(q)
+            w2s.append(sc)
+            del w
+        self.w13q, self.w13s = torch.stack(w13q), torch.stack(w13s)
+        self.w2q, self.w2s = torch.stack(w2q), torch.stack(w2s)
+        del w13q, w2q
+        if P > 1:   # exchange buffers live in the symmetric heap
+            self.all_idx = torch.as_tensor(ctx.iris.empty([T, k], "int32"), device="cuda")
+            self.xrecv = torch.as_tensor(ctx.iris.empty([self.cap, H]), device="cuda").view(torch.bfloat16)
+            self.ybuf = torch.as_tensor(ctx.iris.empty([self.cap, H]), device="cuda").view(torch.bfloat16)
+        self.work = float(T) * k * (2.0 * H * 2 * F + 2.0 * F * H)      # useful FLOP per step, whole job
+        self.scale = 1e12
+        self.launches_per_step = 10 if P == 1 else 16
+        self.gemm_ms = None
+        self.pairs_here = None
+
+    def step(self, i, timed_gemm=None):
+        ctx, s = self.ctx, self.s
+        capi, tk = ctx.capi, ctx.tk
+        E, k = s["E"], s["k"]
+        idx, w = tk.moe_route(self.logits, k)
+        if ctx.world == 1:
+            rop, por, offs, counts = tk.moe_permute(idx, E, 128, 0)
+            xq, xs = tk.moe_quant(self.x, por, 1, k)
+            if timed_gemm:
+                timed_gemm[0].record()
+            y = tk.moe_ffn_fp8(xq, xs, self.w13q, self.w13s, self.w2q, self.w2s, offs)
+            if timed_gemm:
+                timed_gemm[1].record()
+            out = tk.moe_combine(y, idx, rop, w, E, ctx.view)
+            self.pairs_here = counts
+        else:
+            r = ctx.rank
+            capi.allgather(idx, self.all_idx, ctx.dkview)
+            rop, por, offs, counts = tk.moe_permute(self.all_idx, E, 128, self.epr)
+            my_rop = rop[r * self.Tl:(r + 1) * self.Tl]
+            tk.moe_dispatch(self.x, idx, my_rop, self.epr, self.xrecv, ctx.view)
+            xq, xs = tk.moe_quant(self.xrecv, por[r], 2, 1)
+            if timed_gemm:
+                timed_gemm[0].record()
+            y = tk.moe_ffn_fp8(xq, xs, self.w13q, self.w13s, self.w2q, self.w2s, offs[r])
+            if timed_gemm:
+                timed_gemm[1].record()
+            self.ybuf.copy_(y)
+            out = tk.moe_combine(self.ybuf, idx, my_rop, w, self.epr, ctx.view)
+            self.pairs_here = counts[r * self.epr:(r + 1) * self.epr]
+        return out
+
+    def time_gemm(self):
+        import torch
+        e = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        ts = []
+        for i in range(5):
+            self.step(i, e)
+            self.ctx.barrier()
+            ts.append(e[0].elapsed_time(e[1]))
+        ts.sort()
+        self.gemm_ms = ts[len(ts) // 2]
+        self.pairs_rank = int(self.pairs_here.sum().item())
+
+    def e2e_setup(self):
+        import torch
+        self.hx = torch.empty(self.x.shape, dtype=self.x.dtype).pin_memory()
+        self.hx.copy_(self.x)
+        self.hl = torch.empty(self.logits.shape, dtype=self.logits.dtype).pin_memory()
+        self.hl.copy_(self.logits)
+        self.ho = torch.empty(self.Tl, self.s["H"], dtype=torch.bfloat16).pin_memory()
+        return self.hx.numel() * 2 + self.hl.numel() * 4, self.ho.numel() * 2
+
+    def e2e_step(self):
+        self.x.copy_(self.hx, non_blocking=True)
+        self.logits.copy_(self.hl, non_blocking=True)
+        out = self.step(0)
+        self.ho.copy_(out, non_blocking=True)
+
+    def config(self, value):
+        s, P = self.s, self.ctx.world
+        per_pair = 2.0 * s["H"] * 2 * s["F"] + 2.0 * s["F"] * s["H"]
+        c = {"workload": f"fp8 MoE layer, {s['name']}, 128x128 block scales, EP={P}",
+             "l2": f"expert weights ({(self.w13q.numel() + self.w2q.numel()) / 1e6:.0f} MB fp8 on this GPU) exceed L2",
+             "per_gpu_tflops": value / P}
+        if self.gemm_ms:
+            c["grouped_gemm_ms_rank0"] = self.gemm_ms
+            c["grouped_gemm_tflops_rank0"] = self.pairs_rank * per_pair / (self.gemm_ms * 1e-3) / 1e12
+            c["pairs_rank0"] = self.pairs_rank
+        return c
+
+    def roofline(self, ms_step, sustained, peaks, peak_src):
+        s = self.s
+        per_pair = 2.0 * s["H"] * 2 * s["F"] + 2.0 * s["F"] * s["H"]
+        bf16 = peaks.get("bf16_tflops_sustained" if sustained else "bf16_tflops")
+        peak = 2.0 * bf16 if bf16 else None          # no measured fp8 figure: twice the measured bf16 GEMM
+        if self.gemm_ms:
+            ach = self.pairs_rank * per_pair / (self.gemm_ms * 1e-3) / 1e12
+            what = "grouped GEMM kernels alone (rank 0)"
+        else:
+            ach = (self.work / self.ctx.world) / (ms_step * 1e-3) / 1e12
+            what = "whole step"
+        return {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
+                "frac": ach / peak if peak else None, "traffic": load_traffic(self.metric), "of": what,
+                "peak_source": f"2 x {peak_src} cuBLAS bf16 ({'sustained' if sustained else 'burst'}) "
+                               f"taken as the fp8 dense peak"}
+
+
+class Ctx:
+    def __init__(self, rank, world, local_rank):
+        import torch
+        import torch.distributed as dist
+        import iris_py
+        import tk_kernel
+        from __graft_entry__ import load_package
+        self.rank, self.world, self.local_rank = rank, world, local_rank
+        self.torch, self.dist, self.iris_py, self.tk = torch, dist, iris_py, tk_kernel
+        self.capi = load_package().capi
+        self.iris = None
+
+    def make_heap(self, mb):
+        self.iris = self.iris_py.Iris(heap_size_mb=int(mb), verbose=False)
+        assert self.iris.rank() == self.rank and self.iris.world_size() == self.world
+        self.view = self.iris.get_device_view()
+        self.dkview = self.capi.DkView.from_address(self.view._addr())
+
+    def barrier(self):
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, v):
+        t = self.torch.tensor([v], device="cuda", dtype=self.torch.float64)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return t.item()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="gemm_rs",
+                    choices=["gemm_rs", "allreduce", "moe_mixtral", "moe_dsv3"])
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
-    ap.add_argument("--shape", default=None, help="M,N,K override of the workload (profiling runs)")
+    ap.add_argument("--shape", default=None, help="M,N,K override of the GEMM workload (profiling runs)")
+    ap.add_argument("--tokens", type=int, default=0, help="token-count override of a MoE workload (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 0)
 
@@ -188,39 +524,16 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
-    import iris_py
-    import tk_kernel
-
-    P = world
-    assert K_FULL % P == 0 and M_TOK % (P * 128) == 0
-    Kloc = K_FULL // P
-    Mloc = M_TOK // P
-    ws_mb = (2 * M_TOK * N_OUT * 2) // (1 << 20) + 64 if P > 1 else 0
-    iris = iris_py.Iris(heap_size_mb=ws_mb + Mloc * N_OUT * 2 * 2 // (1 << 20) + 64, verbose=False)
-    assert iris.rank() == rank and iris.world_size() == world
-    view = iris.get_device_view()
-
-    # synthetic operands, seeded per rank; several sets so that consecutive steps never hit L2
-    shard_bytes = (M_TOK + N_OUT) * Kloc * 2
-    nsets = max(2, math.ceil(256e6 / shard_bytes))
-    g = torch.Generator(device="cuda").manual_seed(1000 + rank)
-    sets = []
-    for _ in range(nsets):
-        A = torch.randn(M_TOK, Kloc, device="cuda", generator=g).to(torch.bfloat16)
-        Bt = (torch.randn(N_OUT, Kloc, device="cuda", generator=g) / math.sqrt(K_FULL)).to(torch.bfloat16)
-        sets.append((A, Bt))
-    out_t = iris.empty([Mloc, N_OUT], "bfloat16")
-    out = torch.as_tensor(out_t, device="cuda").view(torch.bfloat16)
-
-    def step(i):
-        A, Bt = sets[i % nsets]
-        tk_kernel.gemm_rs(A, Bt, out, view)
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    ctx = Ctx(rank, world, local_rank)
+    if args.workload == "gemm_rs":
+        wl = GemmRs(ctx)
+    elif args.workload == "allreduce":
+        wl = AllReduce(ctx)
+    else:
+        if args.tokens:
+            Moe.SHAPES[args.workload]["T"] = args.tokens
+        wl = Moe(ctx, args.workload)
+    barrier = ctx.barrier
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
@@ -230,13 +543,13 @@ def main():
             time.sleep(0.05)
     barrier()
     for i in range(args.warmup):
-        step(i)
+        wl.step(i)
     barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_clock0 = time.time()
     ev0.record()
     for i in range(args.steps):
-        step(i)
+        wl.step(i)
     ev1.record()
     barrier()
     ms_total = ev0.elapsed_time(ev1)
@@ -256,94 +569,67 @@ def main():
         if go.item() == 0.0:
             break
         for i in range(10):
-            step(i)
+            wl.step(i)
         extra += 10
         torch.cuda.synchronize()
     barrier()
     clocks = sampler.stop(t_clock0, time.time()) if sampler else None
     if clocks is not None:
         clocks["extended_by_untimed_steps"] = extra if clocks_extended else 0
-    status = tk_kernel.device_status()
+    status = ctx.tk.device_status()
     assert status[0] == 0, f"device-side wait timed out: {status}"
-    t = torch.tensor([ms_total], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = t.item() / args.steps
-    flop_total = 2.0 * M_TOK * N_OUT * K_FULL
-    value = flop_total / (ms_step * 1e-3) / 1e12
+    ms_step = ctx.max_over_ranks(ms_total) / args.steps
+    value = wl.work / (ms_step * 1e-3) / wl.scale
+
+    if isinstance(wl, AllReduce):
+        wl.time_each()
+    if isinstance(wl, Moe):
+        wl.time_gemm()
 
     e2e_value = e2e_ms = None
     h2d = d2h = 0
     if not args.no_e2e:
-        # ---- end to end through the Python entry point with host operands
-        hA = torch.empty(M_TOK, Kloc, dtype=torch.bfloat16).pin_memory()
-        hB = torch.empty(N_OUT, Kloc, dtype=torch.bfloat16).pin_memory()
-        hA.copy_(sets[0][0])
-        hB.copy_(sets[0][1])
-        hO = torch.empty(Mloc, N_OUT, dtype=torch.bfloat16).pin_memory()
-        dA, dB = torch.empty_like(sets[0][0]), torch.empty_like(sets[0][1])
-
-        def e2e_step():
-            dA.copy_(hA, non_blocking=True)
-            dB.copy_(hB, non_blocking=True)
-            tk_kernel.gemm_rs(dA, dB, out, view)
-            hO.copy_(out, non_blocking=True)
-
-        e2e_step()
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.e2e_steps):
-            e2e_step()
-        e1.record()
-        barrier()
-        te = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        e2e_ms = te.item() / args.e2e_steps
-        e2e_value = flop_total / (e2e_ms * 1e-3) / 1e12
-        h2d = (hA.numel() + hB.numel()) * 2
-        d2h = hO.numel() * 2
+        sizes = wl.e2e_setup()
+        if sizes is not None:
+            h2d, d2h = sizes
+            barrier()
+            wl.e2e_step()
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.e2e_steps):
+                wl.e2e_step()
+            e1.record()
+            barrier()
+            e2e_ms = ctx.max_over_ranks(e0.elapsed_time(e1)) / args.e2e_steps
+            e2e_value = wl.work / (e2e_ms * 1e-3) / wl.scale
+    status = ctx.tk.device_status()
+    assert status[0] == 0, f"device-side wait timed out: {status}"
 
     if rank == 0:
         peaks, peak_src = load_peaks()
-        timed_s = ms_step * args.steps * 1e-3
-        sustained = timed_s >= 1.0
-        peak = peaks.get("bf16_tflops_sustained" if sustained else "bf16_tflops")
-        achieved = (flop_total / P) / (ms_step * 1e-3) / 1e12     # per GPU, per launch
-        traffic = None
-        prof = ROOT / "profiles" / "traffic.json"
-        if prof.exists():
-            try:
-                traffic = json.loads(prof.read_text()).get(f"gemm_rs_p{P}")
-            except Exception:
-                traffic = None
+        sustained = ms_step * args.steps * 1e-3 >= 1.0
         line = {
-            "metric": "gemm_rs_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": P,
+            "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "higher_is_better": True, "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype,
             "data": "synthetic",
-            "config": {"workload": f"gemm_rs M={M_TOK} N={N_OUT} K={K_FULL} K-sharded over {P} GPU(s), "
-                                   f"out rows reduce-scattered (Llama-70B MLP down-proj shape)",
-                       "l2": f"{nsets} operand sets of {shard_bytes / 1e6:.0f} MB rotated: "
-                             f"{(nsets - 1) * shard_bytes / 1e6:.0f} MB of other operands pass between two "
-                             f"uses of a set (L2 is 126 MB)",
-                       "per_gpu_tflops": value / P},
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak if peak else None, "traffic": traffic,
-                         "peak_source": f"{peak_src} ({'sustained' if sustained else 'burst'} cuBLAS bf16)"},
-            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+            "config": wl.config(value),
+            "roofline": wl.roofline(ms_step, sustained, peaks, peak_src),
+            "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": args.e2e_steps},
-            "gpu_launches": args.steps,
+            "gpu_launches": args.steps * wl.launches_per_step,
             "clocks": clocks,
         }
-        if P == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and isinstance(wl, GemmRs):
             tf, threads, desc, dt = cpu_reference_tflops()
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
                                     "sample": desc, "seconds": dt}
         print(json.dumps(line), flush=True)
     barrier()
-    del out, out_t, view, iris
+    del wl
+    ctx.view = ctx.dkview = None
+    ctx.iris = None
     if world > 1:
         dist.destroy_process_group()
 

@@ -60,6 +60,7 @@ struct GroupedArgs {
     float* hs;           // gated out scales [R/128, F/128]
     __nv_bfloat16* y;    // plain out [R, N]
     unsigned* status;
+    long long* dbg;  // [gridDim.x][DBG_SLOTS] stall counters, or null
 };
 
 enum : unsigned { GS_EMPTY = 32, GS_FULL = 33, GS_TEMPTY = 34, GS_TFULL = 35, GS_EPI = 36 };
@@ -80,6 +81,24 @@ struct TileWalk {
         return true;
     }
 };
+
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
+    unsigned long long v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(__float_as_uint(lo)), "r"(__float_as_uint(hi)));
+    return v;
+}
+// acc.{lo,hi} += {x0,x1} * s.{lo,hi}: one two-wide fp32 FMA
+__device__ __forceinline__ void fma_f32x2(unsigned long long& acc, uint32_t x0, uint32_t x1,
+                                          unsigned long long s) {
+    unsigned long long v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(x0), "r"(x1));
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(v), "l"(s));
+}
+// First TMEM column (inside a 256-column buffer) of this thread's chunk c (0..3)
+template <bool GATED>
+__device__ __forceinline__ int chunk_col(int c, int h) {
+    return GATED ? ((c >> 1) * 128 + h * 64 + (c & 1) * 32) : (h * 128 + c * 32);
+}
 
 template <bool GATED>
 __global__ void __launch_bounds__(G_THREADS, 1)
@@ -104,6 +123,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const WaitCtx wc{g.status, abort_sm};
+    const long long dbg_t0 = clock64();
 
     for (int e = threadIdx.x; e <= g.E; e += blockDim.x) offs_sm[e] = g.offsets[e];
     if (threadIdx.x == 0) {
@@ -182,15 +202,23 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
             uint32_t ph = 0;
             unsigned kbc = 0;  // K blocks issued so far: TMEM buffer = kbc & 1
             bool ok = true;
+            long long dbg_tmem = 0, dbg_full = 0;
             int e, row0, n;
             for (int t = blockIdx.x; ok && walk.locate(t, e, row0, n); t += gridDim.x) {
                 for (int kb = 0; kb < g.num_kb; ++kb, ++kbc) {
                     const int buf = kbc & 1;
-                    if (!mbar_wait(bar_tempty + 8 * buf, ((kbc >> 1) & 1) ^ 1, wc, GS_TEMPTY, t) ||
-                        !mbar_wait(bar_full + 8 * s, ph, wc, GS_FULL, t)) {
+                    long long c0 = clock64();
+                    if (!mbar_wait(bar_tempty + 8 * buf, ((kbc >> 1) & 1) ^ 1, wc, GS_TEMPTY, t)) {
                         ok = false;
                         break;
                     }
+                    dbg_tmem += clock64() - c0;
+                    c0 = clock64();
+                    if (!mbar_wait(bar_full + 8 * s, ph, wc, GS_FULL, t)) {
+                        ok = false;
+                        break;
+                    }
+                    dbg_full += clock64() - c0;
                     tc_fence_after();
                     const uint32_t sa = ring + s * G_STAGE_BYTES;
                     const uint64_t da = umma_desc_sw128(sa);
@@ -207,6 +235,10 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
                     }
                 }
             }
+            if (g.dbg != nullptr) {
+                g.dbg[blockIdx.x * DBG_SLOTS + DBG_MMA_WAIT_TMEM] = dbg_tmem;
+                g.dbg[blockIdx.x * DBG_SLOTS + DBG_MMA_WAIT_FULL] = dbg_full;
+            }
         }
     } else {
         // ---------------------------------------------------------------- promotion + epilogue
@@ -216,11 +248,13 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
         const int KB = g.num_kb;
         unsigned kbc = 0;
         unsigned tiles_done = 0;
+        long long dbg_acc = 0, dbg_tail = 0;
         int e, row0, n;
         for (int t = blockIdx.x; walk.locate(t, e, row0, n); t += gridDim.x, ++tiles_done) {
-            float acc[128];
+            // 128 fp32 accumulators as 64 packed pairs, so that promotion can use the two-wide FMA
+            unsigned long long acc2[64];
 #pragma unroll
-            for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+            for (int i = 0; i < 64; ++i) acc2[i] = 0ull;
             const float* sa_p = g.xs + static_cast<size_t>(row0 / GM) * KB;
             const float* sb0_p;
             const float* sb1_p;
@@ -237,28 +271,46 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
                 const float sa = __ldg(sa_p + kb);
                 const float s0 = sa * __ldg(sb0_p + kb);
                 const float s1 = GATED ? sa * __ldg(sb1_p + kb) : s0;
+                const unsigned long long s0p = pack_f32x2(s0, s0), s1p = pack_f32x2(s1, s1);
+                const long long c0 = clock64();
                 if (!__all_sync(0xffffffffu, mbar_wait(bar_tfull + 8 * buf, (kbc >> 1) & 1, wc, GS_TFULL, t))) {
                     ok = false;
                     break;
                 }
+                dbg_acc += clock64() - c0;
                 tc_fence_after();
                 const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * GN;
+                // gated: chunks 0,1 = gate columns h*64.., chunks 2,3 = up columns 128 + h*64..
+                // A TMEM load takes a few hundred cycles and tcgen05.wait::ld waits for all of
+                // them, so the loads go out two at a time: two round trips per K block, not four.
+                uint32_t ra[32], rb[32];
+                tmem_ld_32x32b_x32(t_row + chunk_col<GATED>(0, h), ra);
+                tmem_ld_32x32b_x32(t_row + chunk_col<GATED>(1, h), rb);
+                tmem_ld_wait();
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    // gated: chunks 0,1 = gate columns h*64.., chunks 2,3 = up columns 128 + h*64..
-                    const int col = GATED ? ((c >> 1) * 128 + h * 64 + (c & 1) * 32) : (h * 128 + c * 32);
-                    uint32_t r[32];
-                    tmem_ld_32x32b_x32(t_row + col, r);
-                    tmem_ld_wait();
-                    const float sc = (GATED && c >= 2) ? s1 : s0;
+                for (int i = 0; i < 16; ++i) fma_f32x2(acc2[i], ra[2 * i], ra[2 * i + 1], s0p);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(sc, __uint_as_float(r[i]), acc[c * 32 + i]);
-                }
+                for (int i = 0; i < 16; ++i) fma_f32x2(acc2[16 + i], rb[2 * i], rb[2 * i + 1], s0p);
+                tmem_ld_32x32b_x32(t_row + chunk_col<GATED>(2, h), ra);
+                tmem_ld_32x32b_x32(t_row + chunk_col<GATED>(3, h), rb);
+                tmem_ld_wait();
+                // every TMEM read of this buffer has completed: hand it back before the last FMAs
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) fma_f32x2(acc2[32 + i], ra[2 * i], ra[2 * i + 1], s1p);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) fma_f32x2(acc2[48 + i], rb[2 * i], rb[2 * i + 1], s1p);
+            }
+            float acc[128];
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+                acc[2 * i] = __uint_as_float(static_cast<uint32_t>(acc2[i]));
+                acc[2 * i + 1] = __uint_as_float(static_cast<uint32_t>(acc2[i] >> 32));
             }
             if (!ok) break;
+            const long long c_tail = clock64();
 
             const int row = row0 + q * 32 + lane;
             if (GATED) {
@@ -267,7 +319,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
 #pragma unroll
                 for (int i = 0; i < 64; ++i) {
                     const float gv = acc[i];
-                    const float hv = gv / (1.0f + __expf(-gv)) * acc[64 + i];
+                    const float hv = gv * __frcp_rn(1.0f + __expf(-gv)) * acc[64 + i];
                     acc[i] = hv;
                     amax = fmaxf(amax, fabsf(hv));
                 }
@@ -283,6 +335,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
 #pragma unroll
                 for (int w = 1; w < G_EPI_WARPS; ++w) tmax = fmaxf(tmax, red_t[w]);
                 const float scale = tmax > 0.f ? tmax / 448.0f : 1.0f;
+                const float inv_scale = 1.0f / scale;
                 if (ew == 0 && lane == 0)
                     g.hs[static_cast<size_t>(row0 / GM) * (g.N / 128) + n] = scale;
                 uint32_t pk[16];
@@ -291,7 +344,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
                     uint32_t w = 0;
 #pragma unroll
                     for (int b = 0; b < 4; ++b) {
-                        float yv = acc[4 * i + b] / scale;
+                        float yv = acc[4 * i + b] * inv_scale;
                         yv = fminf(fmaxf(yv, -448.0f), 448.0f);
                         w |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(yv, __NV_SATFINITE, __NV_E4M3)) << (8 * b);
                     }
@@ -313,11 +366,17 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
                     *reinterpret_cast<uint4*>(dst + 8 * j) = o;
                 }
             }
+            dbg_tail += clock64() - c_tail;
+        }
+        if (g.dbg != nullptr && ew == 0 && lane == 0) {
+            g.dbg[blockIdx.x * DBG_SLOTS + DBG_EPI_WAIT_ACC] = dbg_acc;
+            g.dbg[blockIdx.x * DBG_SLOTS + DBG_EPI_WAIT_SMEM] = dbg_tail;   // tile epilogue (after the K loop)
         }
     }
 
     tc_fence_before();
     __syncthreads();
+    if (g.dbg != nullptr && threadIdx.x == 0) g.dbg[blockIdx.x * DBG_SLOTS + DBG_TOTAL] = clock64() - dbg_t0;
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
@@ -331,6 +390,14 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
 }
 
 }  // namespace dk
+
+static long long* g_moe_dbg = nullptr;
+
+// Stall accounting as for the bf16 GEMM (see dk_gemm_debug_counters): slots 0-3 and 7 are filled.
+extern "C" int dk_moe_gemm_debug_counters(long long* device_buffer) {
+    g_moe_dbg = device_buffer;
+    return DK_OK;
+}
 
 extern "C" int dk_moe_grouped_gemm_fp8(const void* xq, const float* xs, const void* wq, const float* ws,
                                        const int* offsets, int E, int R, int N, int K, int gated,
@@ -366,6 +433,7 @@ extern "C" int dk_moe_grouped_gemm_fp8(const void* xq, const float* xs, const vo
     g.y = static_cast<__nv_bfloat16*>(out);
     rc = device_status_ptr(&g.status);
     if (rc != DK_OK) return rc;
+    g.dbg = g_moe_dbg;
     int sms = 0;
     rc = sm_count(&sms);
     if (rc != DK_OK) return rc;

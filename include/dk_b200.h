@@ -155,6 +155,8 @@ int dk_gemm_rs_phase(const void* A, const void* Bt, void* out, int M, int N, int
  * for flags / spent summing, and the CTA's total. NULL switches it off (the default).
  */
 int dk_gemm_debug_counters(long long* device_buffer);
+/* The same for the fp8 grouped GEMM (MMA waits, promotion waits, per-tile epilogue, total). */
+int dk_moe_gemm_debug_counters(long long* device_buffer);
 
 /* ------------------------------------------------------------------ all-reduce */
 /*
