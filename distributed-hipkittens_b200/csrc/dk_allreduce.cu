@@ -66,13 +66,17 @@ __device__ __forceinline__ uint4 pack8(const float (&acc)[8]) {
 }
 
 // Meet block `b` of every peer: tell each peer this rank has reached `epoch`, then wait for theirs.
+template <bool RELEASE>
 __device__ __forceinline__ bool block_meet(const ARRank& me, int world, size_t flag_base, int b,
                                            unsigned epoch, const WaitCtx& wc, unsigned site) {
     __syncthreads();
     if (threadIdx.x < world) {
         const int r = threadIdx.x;
-        __threadfence_system();
-        signal_store_release_sys(me.ctrl[r] + flag_base + static_cast<size_t>(b) * DK_MAX_RANKS + me.rank, epoch);
+        // the release store itself orders everything this block did before the __syncthreads above
+        // (cumulativity); a separate system fence next to NVLink traffic costs tens of microseconds
+        unsigned* flag = me.ctrl[r] + flag_base + static_cast<size_t>(b) * DK_MAX_RANKS + me.rank;
+        if (RELEASE) signal_store_release_sys(flag, epoch);
+        else signal_store_relaxed_sys(flag, epoch);
         signal_wait_ge(me.ctrl[me.rank] + flag_base + static_cast<size_t>(b) * DK_MAX_RANKS + r, epoch, wc, site, r);
     }
     __syncthreads();
@@ -87,8 +91,9 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_kernel(const __grid_cons
     if (threadIdx.x == 0) abort_sm = 0;
     const WaitCtx wc{job.status, &abort_sm, job.peer_wait_ns};
 
-    // every peer has entered the kernel, so its input is complete
-    if (!block_meet(me, world, DK_CTRL_AR_START, b, job.epoch, wc, SITE_AR_START)) return;
+    // every peer has entered the kernel, so its input (written by earlier work on its stream) is
+    // complete; this block has published nothing yet, so the arrival flag needs no release
+    if (!block_meet<false>(me, world, DK_CTRL_AR_START, b, job.epoch, wc, SITE_AR_START)) return;
 
     const size_t stride = static_cast<size_t>(gridDim.x) * AR_THREADS;
     if (job.algo == 0) {
@@ -124,7 +129,7 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_kernel(const __grid_cons
     }
 
     // one-shot: peers are done reading this rank's input; two-shot: the peers' pushes have landed
-    block_meet(me, world, DK_CTRL_AR_END, b, job.epoch, wc, SITE_AR_END);
+    block_meet<true>(me, world, DK_CTRL_AR_END, b, job.epoch, wc, SITE_AR_END);
 }
 
 static size_t oneshot_max_bytes(int world) {

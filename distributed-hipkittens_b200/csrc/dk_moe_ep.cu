@@ -37,7 +37,6 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(const BarrierArgs a) {
     const WaitCtx wc{a.status, &abort_sm, a.peer_wait_ns};
     if (threadIdx.x < a.world) {
         const int r = threadIdx.x;
-        __threadfence_system();
         signal_store_release_sys(a.ctrl[r] + DK_CTRL_MOE + a.rank, a.epoch);
         signal_wait_ge(a.ctrl[a.rank] + DK_CTRL_MOE + r, a.epoch, wc, SITE_PEER_BARRIER, r);
     }
