@@ -80,6 +80,7 @@ def _declare(L: C.CDLL) -> None:
     L.dk_gemm_rs_phase.argtypes = [vp, vp, vp, i, i, i, vp, C.POINTER(DkView), C.c_uint, i, i, vp]
     L.dk_allreduce.argtypes = [vp, vp, sz, i, C.POINTER(DkView), vp]
     L.dk_gemm_debug_counters.argtypes = [vp]
+    L.dk_gemm_pair_mode.argtypes = [i]
     L.dk_moe_route.argtypes = [vp, i, i, i, vp, vp, vp]
     L.dk_moe_permute_scratch_bytes.restype = sz
     L.dk_moe_permute_scratch_bytes.argtypes = [i, i, i]

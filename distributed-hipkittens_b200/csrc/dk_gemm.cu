@@ -32,20 +32,29 @@
 #include "dk_host.h"
 #include "dk_ptx.cuh"
 
+#include <cstdlib>
+
 namespace dk {
 
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;
-constexpr int B_BYTES = BN * BK * 2;
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int EPI_BUF_BYTES = 32 * 128;  // 32 rows x 64 bf16 per epilogue warp
 constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;
 constexpr int CTRL_BYTES = 256;
-constexpr int GEMM_SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + CTRL_BYTES;
+// PAIR = 1: one CTA per 128x256 tile. PAIR = 2: a cluster of two CTAs per 256x256 tile
+// (tcgen05.mma.cta_group::2): each CTA holds its 128 rows of A and HALF of the Bt tile, so a stage
+// is 32 KiB instead of 48 and the ring is six stages deep instead of four.
+template <int PAIR>
+struct Cfg {
+    static constexpr int B_ROWS = BN / PAIR;
+    static constexpr int B_BYTES = B_ROWS * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = PAIR == 2 ? 6 : 4;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + CTRL_BYTES;
+};
 constexpr int GEMM_THREADS = 384;  // TMA, MMA, 4 epilogue warps, 6 reducer warps
 constexpr int RED_THREADS = 192;
 constexpr int GROUP_M = 16;
@@ -63,6 +72,7 @@ struct GemmArgs {
     int world, rank;
     int rows_per_rank;  // rows of the output owned by one rank (M when world == 1)
     int m_tile_rot;     // first row-tile visited
+    int group_m;        // row-tiles per raster group
     int epi_mode;       // 0 direct stores, 1 TMA stores
     int phases;         // bit 0: GEMM tiles, bit 1: reduce this rank's rows
     __nv_bfloat16* dst[DK_MAX_RANKS];  // per owner: where this rank's partial (or C) goes
@@ -85,11 +95,13 @@ enum : unsigned {
     SITE_RS_FLAG = 6
 };
 
+// t -> (m, n) in units of the launch's tiles (tiles_m counts tiles of 128 * PAIR rows)
 __device__ __forceinline__ void tile_coords(int t, const GemmArgs& g, int& m, int& n) {
-    const int per_group = GROUP_M * g.tiles_n;
+    const int group_m = g.group_m;
+    const int per_group = group_m * g.tiles_n;
     const int grp = t / per_group;
-    const int first_m = grp * GROUP_M;
-    const int gsz = min(g.tiles_m - first_m, GROUP_M);
+    const int first_m = grp * group_m;
+    const int gsz = min(g.tiles_m - first_m, group_m);
     const int r = t - grp * per_group;
     m = first_m + r % gsz;
     n = r / gsz;
@@ -175,25 +187,32 @@ __device__ __forceinline__ void reduce_tile(const __nv_bfloat16* __restrict__ sr
 
 // W = upper bound of g.world this instantiation serves (2, 4 or 8); it only sizes the reducers'
 // register arrays.
-template <int W>
+template <int W, int PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
+    constexpr int STAGES = Cfg<PAIR>::STAGES;
+    constexpr int STAGE_BYTES = Cfg<PAIR>::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+    // position inside the pair and the pair's place in the grid
+    const int crank = PAIR == 2 ? static_cast<int>(cluster_ctarank()) : 0;
+    const int unit = blockIdx.x / PAIR;     // which tile walker this CTA belongs to
+    const int nunits = gridDim.x / PAIR;
 
     const uint32_t ring = smem_base;
     const uint32_t epi = smem_base + STAGES * STAGE_BYTES;
     uint8_t* ctrl = smem + STAGES * STAGE_BYTES + EPI_BYTES;
     const uint32_t ctrl_u = epi + EPI_BYTES;
     // control block: 8-byte mbarriers, then the TMEM base address and the abort flag
-    const uint32_t bar_full = ctrl_u;                // STAGES
-    const uint32_t bar_empty = ctrl_u + 8 * STAGES;  // STAGES
-    const uint32_t bar_tfull = ctrl_u + 16 * STAGES;        // 2
-    const uint32_t bar_tempty = ctrl_u + 16 * STAGES + 16;  // 2
-    const uint32_t bar_epi = ctrl_u + 16 * STAGES + 32;     // 1
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(ctrl + 16 * STAGES + 48);
-    volatile int* abort_sm = reinterpret_cast<volatile int*>(ctrl + 16 * STAGES + 56);
+    const uint32_t bar_full = ctrl_u;                 // STAGES: this CTA's operands have landed
+    const uint32_t bar_empty = ctrl_u + 8 * STAGES;   // STAGES: the MMAs are done with the stage
+    const uint32_t bar_pfull = ctrl_u + 16 * STAGES;  // STAGES: (leader) the peer's operands landed
+    const uint32_t bar_tfull = ctrl_u + 24 * STAGES;        // 2
+    const uint32_t bar_tempty = ctrl_u + 24 * STAGES + 16;  // 2
+    const uint32_t bar_epi = ctrl_u + 24 * STAGES + 32;     // 1
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(ctrl + 24 * STAGES + 40);
+    volatile int* abort_sm = reinterpret_cast<volatile int*>(ctrl + 24 * STAGES + 48);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -207,10 +226,11 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
+            mbar_init(bar_pfull + 8 * s, 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(bar_tfull + 8 * a, 1);
-            mbar_init(bar_tempty + 8 * a, 128);
+            mbar_init(bar_tempty + 8 * a, 128 * PAIR);  // the leader hears both CTAs' epilogues
         }
         mbar_init(bar_epi, 4);
         fence_mbar_init();
@@ -218,11 +238,16 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
         tma_prefetch_desc(&maps.b);
     }
     if (warp == 1 && do_gemm) {
-        tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
-        tmem_relinquish<1>();
+        tmem_alloc<PAIR>(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+        tmem_relinquish<PAIR>();
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR == 2) {
+        // both CTAs' barriers exist before either signals the other's
+        cluster_arrive();
+        cluster_wait();
+    }
     tc_fence_after();
     const uint32_t tmem_base = do_gemm ? *tmem_slot : 0u;
 
@@ -233,37 +258,63 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                 int s = 0;
                 uint32_t ph = 0;
                 bool ok = true;
-                for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                long long dbg_prod = 0;
+                for (int t = unit; t < num_tiles && ok; t += nunits) {
                     int m, n;
                     tile_coords(t, g, m, n);
+                    m = m * PAIR + crank;  // this CTA's 128-row tile
                     for (int kb = 0; kb < g.num_kb; ++kb) {
+                        const long long c0 = clock64();
                         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, wc, SITE_EMPTY, t)) {
                             ok = false;
                             break;
                         }
+                        dbg_prod += clock64() - c0;
                         const uint32_t full = bar_full + 8 * s;
                         mbar_expect_tx(full, STAGE_BYTES);
                         const uint32_t sa = ring + s * STAGE_BYTES;
                         tma_load_2d(sa, &maps.a, full, kb * BK, m * BM);
-                        tma_load_2d(sa + A_BYTES, &maps.b, full, kb * BK, n * BN);
+                        // a pair splits the 256 rows of the Bt tile between its two CTAs
+                        tma_load_2d(sa + A_BYTES, &maps.b, full, kb * BK, n * BN + crank * Cfg<PAIR>::B_ROWS);
                         if (++s == STAGES) {
                             s = 0;
                             ph ^= 1;
                         }
                     }
                 }
+                // plain launches have no reducers: their slot carries the producer's wait for free stages
+                if (g.dbg != nullptr && g.world == 1) g.dbg[blockIdx.x * DBG_SLOTS + DBG_RED_WORK] = dbg_prod;
             }
         } else if (warp == 1) {
             // ------------------------------------------------ MMA issuer
-            if (lane == 0) {
-                constexpr uint32_t idesc = umma_idesc(1, 1, BM, BN);
+            if (lane == 0 && crank != 0) {
+                // follower of a pair: it issues no MMAs; it tells the leader when its own half of
+                // a stage has landed (plain loads cannot signal a barrier in another CTA)
+                int s = 0;
+                uint32_t ph = 0;
+                const long long total_kb = static_cast<long long>((num_tiles - unit + nunits - 1) / nunits) * g.num_kb;
+                long long dbg_relay = 0;
+                for (long long i = 0; i < total_kb; ++i) {
+                    const long long c0 = clock64();
+                    if (!mbar_wait(bar_full + 8 * s, ph, wc, SITE_FULL, static_cast<unsigned>(i))) break;
+                    dbg_relay += clock64() - c0;
+                    mbar_arrive_cluster(mapa_shared(bar_pfull + 8 * s, 0));
+                    if (++s == STAGES) {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+                if (g.dbg != nullptr) g.dbg[blockIdx.x * DBG_SLOTS + DBG_MMA_WAIT_FULL] = dbg_relay;
+            }
+            if (lane == 0 && crank == 0) {
+                constexpr uint32_t idesc = umma_idesc(1, 1, BM * PAIR, BN);
                 int s = 0;
                 uint32_t ph = 0;
                 int acc = 0;
                 uint32_t acc_ph = 0;
                 bool ok = true;
-                long long dbg_mma_tmem = 0, dbg_mma_full = 0;
-                for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                long long dbg_mma_tmem = 0, dbg_mma_full = 0, dbg_mma_pfull = 0;
+                for (int t = unit; t < num_tiles && ok; t += nunits) {
                     long long c0 = clock64();
                     if (!mbar_wait(bar_tempty + 8 * acc, acc_ph ^ 1, wc, SITE_TMEM_EMPTY, t)) break;
                     dbg_mma_tmem += clock64() - c0;
@@ -276,6 +327,14 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                             break;
                         }
                         dbg_mma_full += clock64() - c0;
+                        if (PAIR == 2) {
+                            c0 = clock64();
+                            if (!mbar_wait(bar_pfull + 8 * s, ph, wc, SITE_FULL, t)) {
+                                ok = false;
+                                break;
+                            }
+                            dbg_mma_pfull += clock64() - c0;
+                        }
                         tc_fence_after();
                         const uint32_t sa = ring + s * STAGE_BYTES;
                         const uint64_t da = umma_desc_sw128(sa);
@@ -284,22 +343,26 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                         for (int k = 0; k < BK / UMMA_K; ++k) {
                             // +32 bytes along K inside the 128-byte swizzle row = +2 in the
                             // descriptor's 16-byte address units
-                            umma_f16<1>(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                            umma_f16<PAIR>(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
                         }
-                        umma_commit<1>(bar_empty + 8 * s);
+                        // the stage is free in BOTH CTAs once these MMAs have read it
+                        if (PAIR == 2) umma_commit_pair(bar_empty + 8 * s, 3);
+                        else umma_commit<1>(bar_empty + 8 * s);
                         if (++s == STAGES) {
                             s = 0;
                             ph ^= 1;
                         }
                     }
                     if (!ok) break;
-                    umma_commit<1>(bar_tfull + 8 * acc);
+                    if (PAIR == 2) umma_commit_pair(bar_tfull + 8 * acc, 3);
+                    else umma_commit<1>(bar_tfull + 8 * acc);
                     acc ^= 1;
                     if (acc == 0) acc_ph ^= 1;
                 }
                 if (g.dbg != nullptr) {
                     g.dbg[blockIdx.x * DBG_SLOTS + DBG_MMA_WAIT_TMEM] = dbg_mma_tmem;
                     g.dbg[blockIdx.x * DBG_SLOTS + DBG_MMA_WAIT_FULL] = dbg_mma_full;
+                    if (g.world == 1) g.dbg[blockIdx.x * DBG_SLOTS + DBG_RED_WAIT_FLAG] = dbg_mma_pfull;
                 }
             }
         } else if (warp < 6) {
@@ -311,9 +374,10 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
             uint32_t acc_ph = 0;
             uint32_t epi_ph = 0;
             long long dbg_acc = 0, dbg_smem = 0, dbg_landed = 0, dbg_signal = 0, dbg_drain = 0;
-            for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+            for (int t = unit; t < num_tiles; t += nunits) {
                 int m, n;
                 tile_coords(t, g, m, n);
+                m = m * PAIR + crank;  // this CTA's 128-row tile
                 const int owner = (m * BM) / g.rows_per_rank;
                 const int row0 = m * BM - owner * g.rows_per_rank + q * 32;  // row inside dst
                 // the whole warp takes the same branch: tcgen05.ld below is warp-collective
@@ -383,9 +447,10 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                         }
                     }
                 }
-                // accumulator drained: hand the TMEM buffer back to the MMA warp
+                // accumulator drained: hand the TMEM buffer back to the (leader's) MMA warp
                 tc_fence_before();
-                mbar_arrive(bar_tempty + 8 * acc);
+                if (PAIR == 2 && crank != 0) mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * acc, 0));
+                else mbar_arrive(bar_tempty + 8 * acc);
                 acc ^= 1;
                 if (acc == 0) acc_ph ^= 1;
 
@@ -429,9 +494,10 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
         const int rt = threadIdx.x - (GEMM_THREADS - RED_THREADS);
         const size_t slot_elems = static_cast<size_t>(g.rows_per_rank) * g.tiles_n * BN;
         long long dbg_flag = 0, dbg_work = 0;
-        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        for (int t = unit; t < num_tiles; t += nunits) {
             int m, n;
             tile_coords(t, g, m, n);
+            m = m * PAIR + crank;
             if ((m * BM) / g.rows_per_rank != g.rank) continue;
             long long c0 = clock64();
             const int tm = (m * BM - g.rank * g.rows_per_rank) / BM;
@@ -455,6 +521,11 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
 
     tc_fence_before();
     __syncthreads();
+    if (PAIR == 2) {
+        // neither CTA leaves (or frees the pair's TMEM) while the other may still signal it
+        cluster_arrive();
+        cluster_wait();
+    }
     if (g.dbg != nullptr && threadIdx.x == 0) g.dbg[blockIdx.x * DBG_SLOTS + DBG_TOTAL] = clock64() - dbg_t0;
     if (warp == 1 && do_gemm) {
         __syncwarp();
@@ -465,7 +536,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
             while (globaltimer_ns() - t0 < 200000ull) {
             }
         }
-        tmem_dealloc<1>(tmem_base, TMEM_COLS);
+        tmem_dealloc<PAIR>(tmem_base, TMEM_COLS);
     }
 }
 
@@ -483,25 +554,55 @@ static int check_gemm_args(const void* A, const void* Bt, void* C, int M, int N,
     return DK_OK;
 }
 
-template <int W>
+template <int W, int PAIR>
 static int launch_gemm_w(const GemmMaps& maps, const GemmArgs& args, int grid, cudaStream_t stream) {
     static bool attr_set[64] = {false};
     int dev = 0;
     DK_CUDA_OK(cudaGetDevice(&dev));
     if (!attr_set[dev & 63]) {
-        DK_CUDA_OK(cudaFuncSetAttribute(gemm_bf16_kernel<W>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        GEMM_SMEM_BYTES));
+        DK_CUDA_OK(cudaFuncSetAttribute(gemm_bf16_kernel<W, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        Cfg<PAIR>::SMEM_BYTES));
         attr_set[dev & 63] = true;
     }
-    gemm_bf16_kernel<W><<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(maps, args);
-    DK_CUDA_OK(cudaGetLastError());
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = Cfg<PAIR>::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = PAIR;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    DK_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<W, PAIR>, maps, args));
     return DK_OK;
 }
 
-static int launch_gemm(const GemmMaps& maps, const GemmArgs& args, int grid, cudaStream_t stream) {
-    if (args.world <= 2) return launch_gemm_w<2>(maps, args, grid, stream);
-    if (args.world <= 4) return launch_gemm_w<4>(maps, args, grid, stream);
-    return launch_gemm_w<8>(maps, args, grid, stream);
+// pair != 0 selects the two-CTA kernel; `grid` counts CTAs and is then even.
+static int launch_gemm(const GemmMaps& maps, const GemmArgs& args, int grid, int pair, cudaStream_t stream) {
+    if (pair) {
+        if (args.world <= 2) return launch_gemm_w<2, 2>(maps, args, grid, stream);
+        if (args.world <= 4) return launch_gemm_w<4, 2>(maps, args, grid, stream);
+        return launch_gemm_w<8, 2>(maps, args, grid, stream);
+    }
+    if (args.world <= 2) return launch_gemm_w<2, 1>(maps, args, grid, stream);
+    if (args.world <= 4) return launch_gemm_w<4, 1>(maps, args, grid, stream);
+    return launch_gemm_w<8, 1>(maps, args, grid, stream);
+}
+
+// Two-CTA tiles need whole 256-row tiles (per owner in reduce-scatter mode). The pair kernel is
+// correct but, as measured, slower than the one-CTA kernel (see dk_gemm_pair_mode), so it is used
+// only on request: dk_gemm_pair_mode(1) or DK_GEMM_PAIR=1.
+static int g_pair_mode = -2;  // -2: read DK_GEMM_PAIR on first use; 0 off; 1 on
+static bool use_pair(int M, int rows_per_rank) {
+    if (g_pair_mode == -2) {
+        const char* e = std::getenv("DK_GEMM_PAIR");
+        g_pair_mode = (e && *e && std::atoi(e) == 1) ? 1 : 0;
+    }
+    const bool possible = (M % (2 * BM) == 0) && (rows_per_rank % (2 * BM) == 0);
+    return g_pair_mode == 1 && possible;
 }
 
 int gemm_bf16_impl(const void* A, const void* Bt, void* C, int M, int N, int K, int epilogue,
@@ -512,7 +613,8 @@ int gemm_bf16_impl(const void* A, const void* Bt, void* C, int M, int N, int K, 
     GemmArgs g{};
     rc = make_tmap_2d(&maps.a, A, 2, K, M, static_cast<uint64_t>(K) * 2, BK, BM);
     if (rc != DK_OK) return rc;
-    rc = make_tmap_2d(&maps.b, Bt, 2, K, N, static_cast<uint64_t>(K) * 2, BK, BN);
+    const int pair = use_pair(M, ((M + BM - 1) / BM) * BM) ? 2 : 1;
+    rc = make_tmap_2d(&maps.b, Bt, 2, K, N, static_cast<uint64_t>(K) * 2, BK, BN / pair);
     if (rc != DK_OK) return rc;
     rc = make_tmap_2d(&maps.out[0], C, 2, N, M, static_cast<uint64_t>(N) * 2, 64, 32);
     if (rc != DK_OK) return rc;
@@ -520,12 +622,13 @@ int gemm_bf16_impl(const void* A, const void* Bt, void* C, int M, int N, int K, 
     g.M = M;
     g.N = N;
     g.K = K;
-    g.tiles_m = (M + BM - 1) / BM;
+    g.tiles_m = (M + BM - 1) / BM / pair;   // tiles of 128 * pair rows
+    g.group_m = GROUP_M / pair;
     g.tiles_n = (N + BN - 1) / BN;
     g.num_kb = (K + BK - 1) / BK;
     g.world = 1;
     g.rank = 0;
-    g.rows_per_rank = g.tiles_m * BM;  // one owner
+    g.rows_per_rank = g.tiles_m * pair * BM;  // one owner
     g.m_tile_rot = 0;
     g.epi_mode = epilogue < 0 ? 1 : epilogue;
     g.phases = 1;
@@ -539,7 +642,8 @@ int gemm_bf16_impl(const void* A, const void* Bt, void* C, int M, int N, int K, 
     rc = sm_count(&sms);
     if (rc != DK_OK) return rc;
     const int tiles = g.tiles_m * g.tiles_n;
-    return launch_gemm(maps, g, tiles < sms ? tiles : sms, stream);
+    const int units = sms / pair;   // tile walkers: CTAs, or pairs of CTAs
+    return launch_gemm(maps, g, (tiles < units ? tiles : units) * pair, pair == 2, stream);
 }
 
 // ---- reduce-scatter ---------------------------------------------------------------------------
@@ -585,18 +689,20 @@ int gemm_rs_impl(const void* A, const void* Bt, void* out, int M, int N, int Klo
     GemmArgs g{};
     rc = make_tmap_2d(&maps.a, A, 2, Kloc, M, static_cast<uint64_t>(Kloc) * 2, BK, BM);
     if (rc != DK_OK) return rc;
-    rc = make_tmap_2d(&maps.b, Bt, 2, Kloc, N, static_cast<uint64_t>(Kloc) * 2, BK, BN);
+    const int pair = use_pair(M, mloc) ? 2 : 1;
+    rc = make_tmap_2d(&maps.b, Bt, 2, Kloc, N, static_cast<uint64_t>(Kloc) * 2, BK, BN / pair);
     if (rc != DK_OK) return rc;
     g.M = M;
     g.N = N;
     g.K = Kloc;
-    g.tiles_m = M / BM;
+    g.tiles_m = M / BM / pair;   // tiles of 128 * pair rows
+    g.group_m = GROUP_M / pair;
     g.tiles_n = (N + BN - 1) / BN;
     g.num_kb = (Kloc + BK - 1) / BK;
     g.world = world;
     g.rank = rank;
     g.rows_per_rank = mloc;
-    g.m_tile_rot = ((rank + 1) % world) * (mloc / BM);
+    g.m_tile_rot = ((rank + 1) % world) * (mloc / BM / pair);
     // Pushes to peers always use TMA bulk stores: with direct 16-byte stores to peer memory an
     // 8-GPU run stalled until its peer waits ran out, so that variant is not offered across GPUs.
     (void)epilogue;
@@ -624,10 +730,20 @@ int gemm_rs_impl(const void* A, const void* Bt, void* out, int M, int N, int Klo
     rc = sm_count(&sms);
     if (rc != DK_OK) return rc;
     const int tiles = g.tiles_m * g.tiles_n;
-    return launch_gemm(maps, g, tiles < sms ? tiles : sms, stream);
+    const int units = sms / pair;
+    return launch_gemm(maps, g, (tiles < units ? tiles : units) * pair, pair == 2, stream);
 }
 
 }  // namespace dk
+
+extern "C" int dk_gemm_pair_mode(int mode) {
+    if (mode != 0 && mode != 1) {
+        dk::set_last_error("argument error: mode must be 0 or 1");
+        return DK_ERR_ARG;
+    }
+    dk::g_pair_mode = mode;
+    return DK_OK;
+}
 
 extern "C" int dk_gemm_debug_counters(long long* device_buffer) {
     dk::g_gemm_dbg = device_buffer;

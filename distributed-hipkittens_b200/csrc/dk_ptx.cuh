@@ -289,6 +289,16 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
             "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
             : "memory");
 }
+// Pair form: one commit whose arrive is delivered to the barrier at this offset in every CTA of
+// cta_mask (both CTAs of the pair). This is the tensor pipe's completion signal, not a load.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64"
+        " [%0], %1;" ::"r"(bar),
+        "h"(cta_mask)
+        : "memory");
+}
+
 // TMEM -> registers: this thread's lane (row), 32 consecutive fp32 columns starting at taddr.
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(

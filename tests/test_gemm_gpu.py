@@ -112,3 +112,19 @@ def test_dispatch_micro_reference_call(orc):
     assert ok, err
     assert orc.rel_fro(dC.float().cpu(), orc.gemm_ref(A, B)) <= TOL
     assert tk_kernel.device_status()[0] == 0
+
+
+def test_two_cta_pair_kernel_matches_oracle(capi, orc):
+    """The experimental cta_group::2 variant (clusters of two CTAs per 256x256 tile) gives the same
+    results as the default kernel."""
+    L = capi.lib()
+    capi.check(L.dk_gemm_pair_mode(1))
+    try:
+        for (M, N, K) in [(256, 256, 64), (512, 768, 320), (2048, 4096, 4096), (768, 264, 128)]:
+            A, Bt = orc.make_gemm_inputs(M, N, K, seed=5)
+            C = capi.gemm_bf16(A.cuda(), Bt.cuda())
+            torch.cuda.synchronize()
+            assert capi.device_status()[0] == 0
+            assert orc.rel_fro(C.float().cpu(), orc.gemm_ref(A, Bt)) <= TOL
+    finally:
+        capi.check(L.dk_gemm_pair_mode(0))
