@@ -595,6 +595,16 @@ static int launch_gemm(const GemmMaps& maps, const GemmArgs& args, int grid, int
 // Two-CTA tiles need whole 256-row tiles (per owner in reduce-scatter mode). The pair kernel is
 // correct but, as measured, slower than the one-CTA kernel (see dk_gemm_pair_mode), so it is used
 // only on request: dk_gemm_pair_mode(1) or DK_GEMM_PAIR=1.
+static int group_m_setting() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = std::getenv("DK_GEMM_GROUP_M");
+        v = (e && *e) ? std::atoi(e) : GROUP_M;
+        if (v < 2) v = 2;
+    }
+    return v;
+}
+
 static int g_pair_mode = -2;  // -2: read DK_GEMM_PAIR on first use; 0 off; 1 on
 static bool use_pair(int M, int rows_per_rank) {
     if (g_pair_mode == -2) {
@@ -623,7 +633,7 @@ int gemm_bf16_impl(const void* A, const void* Bt, void* C, int M, int N, int K, 
     g.N = N;
     g.K = K;
     g.tiles_m = (M + BM - 1) / BM / pair;   // tiles of 128 * pair rows
-    g.group_m = GROUP_M / pair;
+    g.group_m = group_m_setting() / pair;
     g.tiles_n = (N + BN - 1) / BN;
     g.num_kb = (K + BK - 1) / BK;
     g.world = 1;
@@ -696,7 +706,7 @@ int gemm_rs_impl(const void* A, const void* Bt, void* out, int M, int N, int Klo
     g.N = N;
     g.K = Kloc;
     g.tiles_m = M / BM / pair;   // tiles of 128 * pair rows
-    g.group_m = GROUP_M / pair;
+    g.group_m = group_m_setting() / pair;
     g.tiles_n = (N + BN - 1) / BN;
     g.num_kb = (Kloc + BK - 1) / BK;
     g.world = world;
