@@ -146,7 +146,7 @@ def cpu_reference_tflops(budget_s: float = 15.0):
                          f"(oracle gemm_ref, torch CPU fp32)"), dt
 
 
-def run_reference(args, rank):
+def run_reference(args, rank, out):
     """--impl reference: the reference's CPU implementation of the path, rank 0 only."""
     if rank != 0:
         return
@@ -168,7 +168,8 @@ def run_reference(args, rank):
         "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    out.write(json.dumps(line) + "\n")
+    out.flush()
 
 
 # ------------------------------------------------------------------------------------ workloads
@@ -497,7 +498,17 @@ class Ctx:
         return t.item()
 
 
+def _claim_stdout():
+    """Keep the real stdout for the one JSON line; whatever libraries print (NCCL's version banner
+    goes to stdout) is sent to stderr instead."""
+    real = os.fdopen(os.dup(1), "w")
+    sys.stdout.flush()
+    os.dup2(2, 1)
+    return real
+
+
 def main():
+    out = _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -520,7 +531,7 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", str(rank)))
     if args.impl == "reference":
-        run_reference(args, rank)
+        run_reference(args, rank, out)
         return
 
     import torch
@@ -634,7 +645,8 @@ def main():
             tf, threads, desc, dt = cpu_reference_tflops()
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
                                     "sample": desc, "seconds": dt}
-        print(json.dumps(line), flush=True)
+        out.write(json.dumps(line) + "\n")
+        out.flush()
     barrier()
     del wl
     ctx.view = ctx.dkview = None
