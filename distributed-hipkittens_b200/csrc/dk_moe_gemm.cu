@@ -13,7 +13,7 @@
 //              (gated: 128 gate rows + the matching 128 up rows), 128-byte swizzle, 4-stage ring
 //   warp 1     MMA issuer: per 128-wide K block, four tcgen05.mma kind::f8f6f4 (128x256x32) into
 //              one of two 256-column TMEM buffers, overwriting (no accumulation across K blocks)
-//   warps 2-9  promotion + epilogue: per K block, tcgen05.ld the partial sums and add them, times
+//   warps 4-11 promotion + epilogue (warps 2-3 only give up their registers): per K block, tcgen05.ld the partial sums and add them, times
 //              sa[m-block,kb] * sb[n-block,kb], to fp32 accumulators kept in registers (each thread
 //              owns one row and 128 of the 256 columns), while the MMA warp fills the other buffer.
 //              Gated: silu(g)*u, tile-wide amax (the 128x128 tile IS one scale block of the
@@ -39,7 +39,7 @@ constexpr int G_STAGE_BYTES = GA_BYTES + GB_BYTES;
 constexpr int G_MAX_E = 256;
 constexpr int G_CTRL_BYTES = 256 + (G_MAX_E + 1) * 4 * 2 + 128;
 constexpr int G_SMEM_BYTES = 1024 + G_STAGES * G_STAGE_BYTES + G_CTRL_BYTES;
-constexpr int G_THREADS = 320;
+constexpr int G_THREADS = 384;   // warp 0 TMA, warp 1 MMA, warps 2-3 idle, warps 4-11 promotion
 constexpr int G_EPI_WARPS = 8;
 
 struct GroupedMaps {
@@ -162,7 +162,15 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
     const uint32_t tmem_base = *tmem_slot;
     TileWalk walk{cum_sm, offs_sm, g.E, g.n_tiles, 0};
 
-    if (warp == 0) {
+    // Registers are re-balanced between the warpgroups: the promotion warps hold 128 accumulators
+    // plus 64 values in flight from TMEM, far above the 168 registers a 384-thread block is
+    // compiled for (a spill in the K loop costs more than anything else in this kernel), while the
+    // TMA and MMA warps need a few dozen.
+    // (Each setmaxnreg sits at the head of the branch it governs: placed before a join it would
+    // bind the code after the join to the smaller value.)
+    if (warp < 4) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+      if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
             int s = 0;
@@ -194,7 +202,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
                 }
             }
         }
-    } else if (warp == 1) {
+      } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc(0, 0, GM, GN);  // e4m3 x e4m3 -> fp32
@@ -240,15 +248,16 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
                 g.dbg[blockIdx.x * DBG_SLOTS + DBG_MMA_WAIT_FULL] = dbg_full;
             }
         }
+      }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
         // ---------------------------------------------------------------- promotion + epilogue
-        const int ew = warp - 2;   // 0..7
+        const int ew = warp - 4;   // 0..7
         const int q = warp & 3;    // TMEM lane quarter of this warp
         const int h = ew >> 2;     // which half of the columns
         const int KB = g.num_kb;
         unsigned kbc = 0;
         unsigned tiles_done = 0;
-        long long dbg_acc = 0, dbg_tail = 0;
         int e, row0, n;
         for (int t = blockIdx.x; walk.locate(t, e, row0, n); t += gridDim.x, ++tiles_done) {
             // 128 fp32 accumulators as 64 packed pairs, so that promotion can use the two-wide FMA
@@ -272,12 +281,10 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
                 const float s0 = sa * __ldg(sb0_p + kb);
                 const float s1 = GATED ? sa * __ldg(sb1_p + kb) : s0;
                 const unsigned long long s0p = pack_f32x2(s0, s0), s1p = pack_f32x2(s1, s1);
-                const long long c0 = clock64();
                 if (!__all_sync(0xffffffffu, mbar_wait(bar_tfull + 8 * buf, (kbc >> 1) & 1, wc, GS_TFULL, t))) {
                     ok = false;
                     break;
                 }
-                dbg_acc += clock64() - c0;
                 tc_fence_after();
                 const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * GN;
                 // gated: chunks 0,1 = gate columns h*64.., chunks 2,3 = up columns 128 + h*64..
@@ -310,7 +317,6 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
                 acc[2 * i + 1] = __uint_as_float(static_cast<uint32_t>(acc2[i] >> 32));
             }
             if (!ok) break;
-            const long long c_tail = clock64();
 
             const int row = row0 + q * 32 + lane;
             if (GATED) {
@@ -366,11 +372,6 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
                     *reinterpret_cast<uint4*>(dst + 8 * j) = o;
                 }
             }
-            dbg_tail += clock64() - c_tail;
-        }
-        if (g.dbg != nullptr && ew == 0 && lane == 0) {
-            g.dbg[blockIdx.x * DBG_SLOTS + DBG_EPI_WAIT_ACC] = dbg_acc;
-            g.dbg[blockIdx.x * DBG_SLOTS + DBG_EPI_WAIT_SMEM] = dbg_tail;   // tile epilogue (after the K loop)
         }
     }
 
