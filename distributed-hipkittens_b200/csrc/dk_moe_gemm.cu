@@ -94,6 +94,11 @@ __device__ __forceinline__ void fma_f32x2(unsigned long long& acc, uint32_t x0, 
     asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(x0), "r"(x1));
     asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(v), "l"(s));
 }
+__device__ __forceinline__ float rcp_approx(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
 // First TMEM column (inside a 256-column buffer) of this thread's chunk c (0..3)
 template <bool GATED>
 __device__ __forceinline__ int chunk_col(int c, int h) {
@@ -260,10 +265,10 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
         unsigned tiles_done = 0;
         int e, row0, n;
         for (int t = blockIdx.x; walk.locate(t, e, row0, n); t += gridDim.x, ++tiles_done) {
-            // 128 fp32 accumulators as 64 packed pairs, so that promotion can use the two-wide FMA
-            unsigned long long acc2[64];
+            // 128 fp32 accumulators per thread: one row, 128 of the tile's 256 columns
+            float acc[128];
 #pragma unroll
-            for (int i = 0; i < 64; ++i) acc2[i] = 0ull;
+            for (int i = 0; i < 128; ++i) acc[i] = 0.f;
             const float* sa_p = g.xs + static_cast<size_t>(row0 / GM) * KB;
             const float* sb0_p;
             const float* sb1_p;
@@ -280,7 +285,6 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
                 const float sa = __ldg(sa_p + kb);
                 const float s0 = sa * __ldg(sb0_p + kb);
                 const float s1 = GATED ? sa * __ldg(sb1_p + kb) : s0;
-                const unsigned long long s0p = pack_f32x2(s0, s0), s1p = pack_f32x2(s1, s1);
                 if (!__all_sync(0xffffffffu, mbar_wait(bar_tfull + 8 * buf, (kbc >> 1) & 1, wc, GS_TFULL, t))) {
                     ok = false;
                     break;
@@ -288,33 +292,30 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
                 tc_fence_after();
                 const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * GN;
                 // gated: chunks 0,1 = gate columns h*64.., chunks 2,3 = up columns 128 + h*64..
-                // A TMEM load takes a few hundred cycles and tcgen05.wait::ld waits for all of
-                // them, so the loads go out two at a time: two round trips per K block, not four.
+                // A warp drains 32 columns in about 100 cycles whatever the batching, and the FMAs
+                // of a K block fill half the FP32 pipe of its scheduler, so the two are interleaved:
+                // while chunk c is folded into the accumulators, chunk c+1 is already on its way.
                 uint32_t ra[32], rb[32];
                 tmem_ld_32x32b_x32(t_row + chunk_col<GATED>(0, h), ra);
                 tmem_ld_32x32b_x32(t_row + chunk_col<GATED>(1, h), rb);
-                tmem_ld_wait();
+                tmem_ld_wait(ra);
+                tmem_ld_wait(rb);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) fma_f32x2(acc2[i], ra[2 * i], ra[2 * i + 1], s0p);
-#pragma unroll
-                for (int i = 0; i < 16; ++i) fma_f32x2(acc2[16 + i], rb[2 * i], rb[2 * i + 1], s0p);
+                for (int i = 0; i < 32; ++i) acc[i] = fmaf(s0, __uint_as_float(ra[i]), acc[i]);
                 tmem_ld_32x32b_x32(t_row + chunk_col<GATED>(2, h), ra);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(s0, __uint_as_float(rb[i]), acc[32 + i]);
                 tmem_ld_32x32b_x32(t_row + chunk_col<GATED>(3, h), rb);
-                tmem_ld_wait();
+                tmem_ld_wait(ra);
+                tmem_ld_wait(rb);
                 // every TMEM read of this buffer has completed: hand it back before the last FMAs
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) fma_f32x2(acc2[32 + i], ra[2 * i], ra[2 * i + 1], s1p);
+                for (int i = 0; i < 32; ++i) acc[64 + i] = fmaf(s1, __uint_as_float(ra[i]), acc[64 + i]);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) fma_f32x2(acc2[48 + i], rb[2 * i], rb[2 * i + 1], s1p);
-            }
-            float acc[128];
-#pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                acc[2 * i] = __uint_as_float(static_cast<uint32_t>(acc2[i]));
-                acc[2 * i + 1] = __uint_as_float(static_cast<uint32_t>(acc2[i] >> 32));
+                for (int i = 0; i < 32; ++i) acc[96 + i] = fmaf(s1, __uint_as_float(rb[i]), acc[96 + i]);
             }
             if (!ok) break;
 
@@ -325,7 +326,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
 #pragma unroll
                 for (int i = 0; i < 64; ++i) {
                     const float gv = acc[i];
-                    const float hv = gv * __frcp_rn(1.0f + __expf(-gv)) * acc[64 + i];
+                    const float hv = gv * rcp_approx(1.0f + __expf(-gv)) * acc[64 + i];
                     acc[i] = hv;
                     amax = fmaxf(amax, fabsf(hv));
                 }
@@ -347,14 +348,12 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    uint32_t w = 0;
-#pragma unroll
-                    for (int b = 0; b < 4; ++b) {
-                        float yv = acc[4 * i + b] * inv_scale;
-                        yv = fminf(fmaxf(yv, -448.0f), 448.0f);
-                        w |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(yv, __NV_SATFINITE, __NV_E4M3)) << (8 * b);
-                    }
-                    pk[i] = w;
+                    // two values per conversion instruction; satfinite clamps to +-448 by itself
+                    const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+                        make_float2(acc[4 * i] * inv_scale, acc[4 * i + 1] * inv_scale), __NV_SATFINITE, __NV_E4M3);
+                    const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+                        make_float2(acc[4 * i + 2] * inv_scale, acc[4 * i + 3] * inv_scale), __NV_SATFINITE, __NV_E4M3);
+                    pk[i] = lo | (hi << 16);
                 }
                 uint8_t* dst = g.hq + static_cast<size_t>(row) * g.N + n * 128 + h * 64;
 #pragma unroll
