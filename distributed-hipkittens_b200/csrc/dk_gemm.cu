@@ -394,7 +394,8 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                     uint32_t r0[32], r1[32];
                     tmem_ld_32x32b_x32(t_acc + c * 64, r0);
                     tmem_ld_32x32b_x32(t_acc + c * 64 + 32, r1);
-                    tmem_ld_wait();
+                    tmem_ld_wait(r0);
+                    tmem_ld_wait(r1);
                     uint32_t p[32];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
