@@ -203,6 +203,24 @@ class GemmRs:
         A, Bt = self.sets[i % self.nsets]
         self.ctx.tk.gemm_rs(A, Bt, self.out, self.ctx.view)
 
+    def check(self):
+        """Relative Frobenius error of the first 64 rows this rank owns against a NCCL sum of the
+        ranks' fp32 partial products (a checker outside the timed region, not part of the path)."""
+        import torch
+        ctx = self.ctx
+        A, Bt = self.sets[0]
+        self.ctx.tk.gemm_rs(A, Bt, self.out, ctx.view)
+        torch.cuda.synchronize()
+        err = 0.0
+        for r in range(ctx.world):
+            rows = slice(r * self.Mloc, r * self.Mloc + 64)
+            p = A[rows].float() @ Bt.float().T
+            if ctx.world > 1:
+                ctx.dist.all_reduce(p)
+            if r == ctx.rank:
+                err = ((self.out[:64].float() - p).norm() / p.norm()).item()
+        return ctx.max_over_ranks(err)
+
     def e2e_setup(self):
         import torch
         A, Bt = self.sets[0]
@@ -274,6 +292,24 @@ class AllReduce:
         for name in ("decode", "prefill"):
             xs, o = self.bufs[name]
             self.ctx.tk.allreduce(xs[i % 2], o, self.ctx.view, -1)
+
+    def check(self):
+        import torch
+        ctx = self.ctx
+        worst = 0.0
+        for name in ("decode", "prefill"):
+            xs, o = self.bufs[name]
+            for algo in ((0, 1) if ctx.world > 1 else (0,)):
+                o.zero_()
+                ctx.barrier()
+                ctx.tk.allreduce(xs[0], o, ctx.view, algo)
+                torch.cuda.synchronize()
+                ref = xs[0].float().clone()
+                if ctx.world > 1:
+                    ctx.dist.all_reduce(ref)
+                worst = max(worst, ((o.float() - ref).norm() / ref.norm()).item())
+                ctx.barrier()
+        return ctx.max_over_ranks(worst)
 
     def time_each(self):
         """Separate timings of the two messages and of both algorithms (reported in config)."""
@@ -520,6 +556,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--shape", default=None, help="M,N,K override of the GEMM workload (profiling runs)")
+    ap.add_argument("--check", action="store_true",
+                    help="also compare one result with a NCCL/torch sum (outside the timed region)")
     ap.add_argument("--tokens", type=int, default=0, help="token-count override of a MoE workload (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 0)
@@ -601,6 +639,9 @@ def main():
     ms_step = ctx.max_over_ranks(ms_total) / args.steps
     value = wl.work / (ms_step * 1e-3) / wl.scale
 
+    check_err = None
+    if args.check and hasattr(wl, "check"):
+        check_err = wl.check()
     if isinstance(wl, AllReduce):
         wl.time_each()
     if isinstance(wl, Moe):
@@ -641,6 +682,8 @@ def main():
             "gpu_launches": args.steps * wl.launches_per_step,
             "clocks": clocks,
         }
+        if check_err is not None:
+            line["check_rel_fro"] = check_err
         if world == 1 and not args.no_cpu_baseline and isinstance(wl, GemmRs):
             tf, threads, desc, dt = cpu_reference_tflops()
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
