@@ -129,3 +129,89 @@ def test_ep_layout_consistent_with_single_rank(orc):
     rp1, ro1, rop1, _ = orc.ep_layout(idx, E, 1)
     rop_s, por_s, offs_s, _ = orc.moe_permute(idx, E)
     assert torch.equal(rp1[0], por_s) and torch.equal(ro1[0], offs_s) and torch.equal(rop1, rop_s)
+
+
+# ---- the plain-C restatement and the Python oracle pin each other ------------------------------
+def _c_oracle():
+    import ctypes as C
+    import subprocess
+    root = Path(__file__).resolve().parents[1] / "oracle"
+    lib = root / "libdk_oracle_c.so"
+    if not lib.exists():
+        subprocess.run(["make", "-C", str(root), "-s"], check=True)
+    return C.CDLL(str(lib))
+
+
+def test_c_oracle_matches_python_oracle(orc):
+    import ctypes as C
+    L = _c_oracle()
+    g = torch.Generator().manual_seed(21)
+    T, E, k = 500, 64, 6
+    logits = torch.randn(T, E, generator=g)
+    logits[7] = 0.25                                   # all equal: lowest indices win
+    logits[9, 3] = logits[9, 40] = 9.0                 # tie at the top
+    idx_c = torch.empty(T, k, dtype=torch.int32)
+    w_c = torch.empty(T, k)
+    L.dk_c_route(C.c_void_p(logits.data_ptr()), T, E, k, C.c_void_p(idx_c.data_ptr()), C.c_void_p(w_c.data_ptr()))
+    idx_p, w_p = orc.moe_route(logits, k)
+    assert torch.equal(idx_c, idx_p)
+    assert torch.allclose(w_c, w_p, rtol=1e-5)
+
+    for seg in (E, E // 4):
+        nseg = E // seg
+        cap = T * k + seg * 127
+        cap = (cap + 127) // 128 * 128
+        rop = torch.empty(T, k, dtype=torch.int32)
+        por = torch.empty(nseg, cap, dtype=torch.int32)
+        offs = torch.empty(nseg, seg + 1, dtype=torch.int32)
+        cnt = torch.empty(E, dtype=torch.int32)
+        L.dk_c_permute(C.c_void_p(idx_p.data_ptr()), T, k, E, 128, seg, cap, C.c_void_p(rop.data_ptr()),
+                       C.c_void_p(por.data_ptr()), C.c_void_p(offs.data_ptr()), C.c_void_p(cnt.data_ptr()))
+        if seg == E:
+            r_rop, r_por, r_offs, r_cnt = orc.moe_permute(idx_p, E, 128)
+            assert torch.equal(rop, r_rop) and torch.equal(offs[0], r_offs) and torch.equal(cnt, r_cnt)
+            assert torch.equal(por[0, :r_por.numel()], r_por)
+        else:
+            recv_pair, recv_offs, r_rop, _ = orc.ep_layout(idx_p, E, nseg)
+            assert torch.equal(rop, r_rop)
+            for d in range(nseg):
+                assert torch.equal(offs[d], recv_offs[d])
+                assert torch.equal(por[d, :recv_pair[d].numel()], recv_pair[d])
+
+    for scale in (1.0, 3e-4, 500.0):
+        x = (torch.randn(256, 384, generator=g) * scale).to(torch.bfloat16)
+        x[:128, :128] = 0
+        q = torch.empty(256, 384, dtype=torch.uint8)
+        s = torch.empty(2, 3)
+        L.dk_c_quant_block128(C.c_void_p(x.view(torch.int16).data_ptr()), 256, 384, C.c_void_p(q.data_ptr()),
+                              C.c_void_p(s.data_ptr()))
+        q_p, s_p = orc.quant_block128(x)
+        assert torch.equal(s, s_p)
+        assert torch.equal(q, q_p)
+
+
+def test_c_e4m3_conversion_exhaustive_against_torch():
+    """Every bf16 bit pattern in [-448, 448] through the C quantiser's e4m3 rounding vs torch's."""
+    import ctypes as C
+    L = _c_oracle()
+    bits = torch.arange(0, 65536, dtype=torch.int32).to(torch.int16)
+    vals = bits.view(torch.bfloat16).float()
+    keep = torch.isfinite(vals) & (vals.abs() <= 448)
+    v = vals[keep]
+    n = (v.numel() // 128) * 128
+    v = v[:n]
+    # scale 1: put the block maximum at exactly 448 so that s == 1 and q == e4m3(x)
+    x = v.reshape(-1, 128).to(torch.bfloat16)
+    pad_rows = (-x.shape[0]) % 128
+    x = torch.cat([x, torch.zeros(pad_rows, 128, dtype=torch.bfloat16)], 0)
+    x[0, 0] = 448.0
+    x[-1 if pad_rows else 0, 1] = 448.0
+    for r0 in range(0, x.shape[0], 128):
+        x[r0, 2] = 448.0
+    q = torch.empty(x.shape, dtype=torch.uint8)
+    s = torch.empty(x.shape[0] // 128, 1)
+    L.dk_c_quant_block128(C.c_void_p(x.view(torch.int16).data_ptr()), x.shape[0], 128, C.c_void_p(q.data_ptr()),
+                          C.c_void_p(s.data_ptr()))
+    assert bool((s == 1.0).all())
+    want = x.float().to(torch.float8_e4m3fn).view(torch.uint8)
+    assert torch.equal(q, want)
