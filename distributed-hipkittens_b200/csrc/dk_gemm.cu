@@ -205,9 +205,8 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
     uint8_t* ctrl = smem + STAGES * STAGE_BYTES + EPI_BYTES;
     const uint32_t ctrl_u = epi + EPI_BYTES;
     // control block: 8-byte mbarriers, then the TMEM base address and the abort flag
-    const uint32_t bar_full = ctrl_u;                 // STAGES: this CTA's operands have landed
+    const uint32_t bar_full = ctrl_u;                 // STAGES: operands landed (a pair: both CTAs', on the leader)
     const uint32_t bar_empty = ctrl_u + 8 * STAGES;   // STAGES: the MMAs are done with the stage
-    const uint32_t bar_pfull = ctrl_u + 16 * STAGES;  // STAGES: (leader) the peer's operands landed
     const uint32_t bar_tfull = ctrl_u + 24 * STAGES;        // 2
     const uint32_t bar_tempty = ctrl_u + 24 * STAGES + 16;  // 2
     const uint32_t bar_epi = ctrl_u + 24 * STAGES + 32;     // 1
@@ -226,7 +225,6 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
-            mbar_init(bar_pfull + 8 * s, 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(bar_tfull + 8 * a, 1);
@@ -271,11 +269,22 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                         }
                         dbg_prod += clock64() - c0;
                         const uint32_t full = bar_full + 8 * s;
-                        mbar_expect_tx(full, STAGE_BYTES);
                         const uint32_t sa = ring + s * STAGE_BYTES;
-                        tma_load_2d(sa, &maps.a, full, kb * BK, m * BM);
-                        // a pair splits the 256 rows of the Bt tile between its two CTAs
-                        tma_load_2d(sa + A_BYTES, &maps.b, full, kb * BK, n * BN + crank * Cfg<PAIR>::B_ROWS);
+                        if (PAIR == 2) {
+                            // both CTAs' loads complete on the LEADER's barrier, which expects the
+                            // bytes of both; the follower's bytes may land before the leader has
+                            // announced them (the phase cannot end before the leader's arrive)
+                            const uint32_t lead_full = mapa_shared(full, 0);
+                            if (crank == 0) mbar_expect_tx(full, 2 * STAGE_BYTES);
+                            tma_load_2d_pair(sa, &maps.a, lead_full, kb * BK, m * BM);
+                            // a pair splits the 256 rows of the Bt tile between its two CTAs
+                            tma_load_2d_pair(sa + A_BYTES, &maps.b, lead_full, kb * BK,
+                                             n * BN + crank * Cfg<PAIR>::B_ROWS);
+                        } else {
+                            mbar_expect_tx(full, STAGE_BYTES);
+                            tma_load_2d(sa, &maps.a, full, kb * BK, m * BM);
+                            tma_load_2d(sa + A_BYTES, &maps.b, full, kb * BK, n * BN);
+                        }
                         if (++s == STAGES) {
                             s = 0;
                             ph ^= 1;
@@ -287,25 +296,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
             }
         } else if (warp == 1) {
             // ------------------------------------------------ MMA issuer
-            if (lane == 0 && crank != 0) {
-                // follower of a pair: it issues no MMAs; it tells the leader when its own half of
-                // a stage has landed (plain loads cannot signal a barrier in another CTA)
-                int s = 0;
-                uint32_t ph = 0;
-                const long long total_kb = static_cast<long long>((num_tiles - unit + nunits - 1) / nunits) * g.num_kb;
-                long long dbg_relay = 0;
-                for (long long i = 0; i < total_kb; ++i) {
-                    const long long c0 = clock64();
-                    if (!mbar_wait(bar_full + 8 * s, ph, wc, SITE_FULL, static_cast<unsigned>(i))) break;
-                    dbg_relay += clock64() - c0;
-                    mbar_arrive_cluster(mapa_shared(bar_pfull + 8 * s, 0));
-                    if (++s == STAGES) {
-                        s = 0;
-                        ph ^= 1;
-                    }
-                }
-                if (g.dbg != nullptr) g.dbg[blockIdx.x * DBG_SLOTS + DBG_MMA_WAIT_FULL] = dbg_relay;
-            }
+            // the follower of a pair issues no MMAs: its operands complete on the leader's barrier
             if (lane == 0 && crank == 0) {
                 constexpr uint32_t idesc = umma_idesc(1, 1, BM * PAIR, BN);
                 int s = 0;
@@ -313,7 +304,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                 int acc = 0;
                 uint32_t acc_ph = 0;
                 bool ok = true;
-                long long dbg_mma_tmem = 0, dbg_mma_full = 0, dbg_mma_pfull = 0;
+                long long dbg_mma_tmem = 0, dbg_mma_full = 0;
                 for (int t = unit; t < num_tiles && ok; t += nunits) {
                     long long c0 = clock64();
                     if (!mbar_wait(bar_tempty + 8 * acc, acc_ph ^ 1, wc, SITE_TMEM_EMPTY, t)) break;
@@ -327,14 +318,6 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                             break;
                         }
                         dbg_mma_full += clock64() - c0;
-                        if (PAIR == 2) {
-                            c0 = clock64();
-                            if (!mbar_wait(bar_pfull + 8 * s, ph, wc, SITE_FULL, t)) {
-                                ok = false;
-                                break;
-                            }
-                            dbg_mma_pfull += clock64() - c0;
-                        }
                         tc_fence_after();
                         const uint32_t sa = ring + s * STAGE_BYTES;
                         const uint64_t da = umma_desc_sw128(sa);
@@ -362,7 +345,6 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                 if (g.dbg != nullptr) {
                     g.dbg[blockIdx.x * DBG_SLOTS + DBG_MMA_WAIT_TMEM] = dbg_mma_tmem;
                     g.dbg[blockIdx.x * DBG_SLOTS + DBG_MMA_WAIT_FULL] = dbg_mma_full;
-                    if (g.world == 1) g.dbg[blockIdx.x * DBG_SLOTS + DBG_RED_WAIT_FLAG] = dbg_mma_pfull;
                 }
             }
         } else if (warp < 6) {
@@ -477,7 +459,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                 g.dbg[blockIdx.x * DBG_SLOTS + DBG_EPI_WAIT_ACC] = dbg_acc;
                 g.dbg[blockIdx.x * DBG_SLOTS + DBG_EPI_WAIT_SMEM] = dbg_smem;
                 g.dbg[blockIdx.x * DBG_SLOTS + DBG_EPI_WAIT_LANDED] = dbg_landed;
-                if ((g.phases & 2) == 0) {
+                if ((g.phases & 2) == 0 && g.world > 1) {
                     // produce-only launches have no reducers: their two slots carry the time spent
                     // draining accumulators and the time spent in fences + flag stores instead
                     g.dbg[blockIdx.x * DBG_SLOTS + DBG_RED_WAIT_FLAG] = dbg_drain;
@@ -593,9 +575,10 @@ static int launch_gemm(const GemmMaps& maps, const GemmArgs& args, int grid, int
     return launch_gemm_w<8, 1>(maps, args, grid, stream);
 }
 
-// Two-CTA tiles need whole 256-row tiles (per owner in reduce-scatter mode). The pair kernel is
-// correct but, as measured, slower than the one-CTA kernel (see dk_gemm_pair_mode), so it is used
-// only on request: dk_gemm_pair_mode(1) or DK_GEMM_PAIR=1.
+// Two-CTA tiles need whole 256-row tiles (per owner in reduce-scatter mode). Where the shape allows
+// it the pair kernel is the default (it needs two thirds of the one-CTA kernel's shared-memory fill
+// bandwidth per flop and has a deeper ring); dk_gemm_pair_mode(0) or DK_GEMM_PAIR=0 selects the
+// one-CTA kernel.
 static int group_m_setting() {
     static int v = -1;
     if (v < 0) {
@@ -606,11 +589,11 @@ static int group_m_setting() {
     return v;
 }
 
-static int g_pair_mode = -2;  // -2: read DK_GEMM_PAIR on first use; 0 off; 1 on
+static int g_pair_mode = -2;  // -2: read DK_GEMM_PAIR on first use; 0 off; 1 on (default)
 static bool use_pair(int M, int rows_per_rank) {
     if (g_pair_mode == -2) {
         const char* e = std::getenv("DK_GEMM_PAIR");
-        g_pair_mode = (e && *e && std::atoi(e) == 1) ? 1 : 0;
+        g_pair_mode = (e && *e && std::atoi(e) == 0) ? 0 : 1;
     }
     const bool possible = (M % (2 * BM) == 0) && (rows_per_rank % (2 * BM) == 0);
     return g_pair_mode == 1 && possible;

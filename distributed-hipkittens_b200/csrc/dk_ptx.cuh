@@ -137,6 +137,17 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, 
         "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y)
         : "memory");
 }
+// The same load issued by either CTA of a cta_group::2 pair: the data lands in the issuing CTA's
+// shared memory, the byte count completes on `cluster_bar`, an mbarrier that may live in the
+// OTHER CTA of the pair (address from mapa). No multicast: one CTA receives the tile.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m,
+                                                 uint32_t cluster_bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(m)), "r"(cluster_bar), "r"(x), "r"(y)
+        : "memory");
+}
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, uint32_t bar,
                                             int x, int y, int z) {
     asm volatile(

@@ -149,11 +149,12 @@ int dk_gemm_rs_phase(const void* A, const void* Bt, void* out, int M, int N, int
 /* (`epilogue` is honoured for world == 1 only: pushes to peers always use TMA bulk stores.) */
 
 /*
- * Experimental: mode 1 makes dk_gemm_bf16 / dk_gemm_rs use clusters of two CTAs per 256x256 tile
- * (tcgen05.mma.cta_group::2: each CTA stages its 128 rows of A and half of the Bt tile, six-stage
- * ring) whenever M (and the rows per rank) are multiples of 256. Results are identical; as measured
- * on B200 it runs at less than half the speed of the default one-CTA kernel, so the default is 0
- * (DK_GEMM_PAIR=1 in the environment also selects it).
+ * Mode 1 (the default; DK_GEMM_PAIR=0 in the environment selects 0) makes dk_gemm_bf16 / dk_gemm_rs
+ * use clusters of two CTAs per 256x256 tile (tcgen05.mma.cta_group::2: each CTA stages its 128
+ * rows of A and half of the Bt tile in a six-stage ring, both CTAs' TMA loads complete on the
+ * leader's mbarrier) whenever M (and the rows per rank) are multiples of 256; other shapes, and
+ * mode 0, use the one-CTA kernel (128x256 tiles, four stages). Results are identical. No reference
+ * counterpart.
  */
 int dk_gemm_pair_mode(int mode);
 /*

@@ -114,17 +114,27 @@ def test_dispatch_micro_reference_call(orc):
     assert tk_kernel.device_status()[0] == 0
 
 
-def test_two_cta_pair_kernel_matches_oracle(capi, orc):
-    """The experimental cta_group::2 variant (clusters of two CTAs per 256x256 tile) gives the same
-    results as the default kernel."""
+@pytest.mark.parametrize("mode", [1, 0])
+def test_pair_and_single_cta_kernels_match_oracle(capi, orc, mode):
+    """The cta_group::2 kernel (clusters of two CTAs per 256x256 tile, the default where M allows)
+    and the one-CTA kernel give the same results; shapes with M % 256 != 0 fall back by themselves."""
     L = capi.lib()
-    capi.check(L.dk_gemm_pair_mode(1))
+    capi.check(L.dk_gemm_pair_mode(mode))
     try:
-        for (M, N, K) in [(256, 256, 64), (512, 768, 320), (2048, 4096, 4096), (768, 264, 128)]:
+        outs = []
+        for (M, N, K) in [(256, 256, 64), (512, 768, 320), (2048, 4096, 4096), (768, 264, 128),
+                          (384, 512, 192)]:
             A, Bt = orc.make_gemm_inputs(M, N, K, seed=5)
             C = capi.gemm_bf16(A.cuda(), Bt.cuda())
             torch.cuda.synchronize()
             assert capi.device_status()[0] == 0
             assert orc.rel_fro(C.float().cpu(), orc.gemm_ref(A, Bt)) <= TOL
+            outs.append(C)
+        # bit-identical between the two kernels: same K order, same fp32 accumulation
+        capi.check(L.dk_gemm_pair_mode(1 - mode))
+        A, Bt = orc.make_gemm_inputs(512, 768, 320, seed=5)
+        C2 = capi.gemm_bf16(A.cuda(), Bt.cuda())
+        torch.cuda.synchronize()
+        assert torch.equal(C2, outs[1])
     finally:
-        capi.check(L.dk_gemm_pair_mode(0))
+        capi.check(L.dk_gemm_pair_mode(1))

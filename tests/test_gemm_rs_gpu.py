@@ -20,9 +20,19 @@ def _fake_job(capi, world, M, N):
     return buf, views, ws
 
 
-@pytest.mark.parametrize("epilogue", [0, 1])
-@pytest.mark.parametrize("world,M,N,K", [(2, 512, 512, 256), (4, 1024, 768, 512), (8, 2048, 264, 1024)])
-def test_gemm_rs_all_ranks_on_one_gpu(capi, orc, world, M, N, K, epilogue):
+@pytest.fixture
+def pair_mode(capi, request):
+    """Two-CTA (1, the default) or one-CTA (0) kernel for the test; the default is restored."""
+    capi.check(capi.lib().dk_gemm_pair_mode(request.param))
+    yield request.param
+    capi.check(capi.lib().dk_gemm_pair_mode(1))
+
+
+@pytest.mark.parametrize("pair_mode", [1, 0], indirect=True)
+@pytest.mark.parametrize("world,M,N,K", [(2, 512, 512, 256), (4, 1024, 768, 512), (8, 2048, 264, 1024),
+                                         (2, 256, 512, 128), (4, 2048, 1024, 256)])
+def test_gemm_rs_all_ranks_on_one_gpu(capi, orc, world, M, N, K, pair_mode):
+    epilogue = -1
     A, Bt = orc.make_gemm_inputs(M, N, K, seed=0)
     As, Bs = orc.shard_k(A, Bt, world)
     want = orc.gemm_rs_ref(As, Bs)
