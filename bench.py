@@ -458,6 +458,9 @@ class Moe:
         ts.sort()
         self.gemm_ms = ts[len(ts) // 2]
         self.pairs_rank = int(self.pairs_here.sum().item())
+        # the step is timed as the max over ranks: say what the most loaded rank carried
+        self.pairs_max = int(self.ctx.max_over_ranks(float(self.pairs_rank)))
+        self.gemm_ms_max = self.ctx.max_over_ranks(self.gemm_ms)
 
     def e2e_setup(self):
         import torch
@@ -484,6 +487,8 @@ class Moe:
             c["grouped_gemm_ms_rank0"] = self.gemm_ms
             c["grouped_gemm_tflops_rank0"] = self.pairs_rank * per_pair / (self.gemm_ms * 1e-3) / 1e12
             c["pairs_rank0"] = self.pairs_rank
+            c["pairs_max_rank"] = self.pairs_max
+            c["grouped_gemm_ms_max_rank"] = self.gemm_ms_max
         return c
 
     def roofline(self, ms_step, sustained, peaks, peak_src):
