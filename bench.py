@@ -232,11 +232,45 @@ class GemmRs:
         self.dA, self.dB = torch.empty_like(A), torch.empty_like(Bt)
         return (self.hA.numel() + self.hB.numel()) * 2, self.hO.numel() * 2
 
+    E2E_CHUNKS = 8
+
     def e2e_step(self):
-        self.dA.copy_(self.hA, non_blocking=True)
-        self.dB.copy_(self.hB, non_blocking=True)
-        self.ctx.tk.gemm_rs(self.dA, self.dB, self.out, self.ctx.view)
-        self.hO.copy_(self.out, non_blocking=True)
+        import torch
+        if self.ctx.world > 1:
+            self.dA.copy_(self.hA, non_blocking=True)
+            self.dB.copy_(self.hB, non_blocking=True)
+            self.ctx.tk.gemm_rs(self.dA, self.dB, self.out, self.ctx.view)
+            self.hO.copy_(self.out, non_blocking=True)
+            return
+        # One GPU: the step is bound by the host link, so the calls are pipelined the way a user
+        # with host-resident operands would: Bt goes in first, then A in row chunks on a copy
+        # stream; each chunk's GEMM starts when its rows have landed, and its rows of the result go
+        # back on a third stream while the next chunk is still coming in.
+        if not hasattr(self, "s_in"):
+            self.s_in, self.s_out = torch.cuda.Stream(), torch.cuda.Stream()
+            n = self.E2E_CHUNKS
+            self.ev_in = [torch.cuda.Event() for _ in range(n)]
+            self.ev_mm = [torch.cuda.Event() for _ in range(n)]
+        cur = torch.cuda.current_stream()
+        n = self.E2E_CHUNKS
+        rows = M_TOK // n
+        self.s_in.wait_stream(cur)        # the previous step's GEMMs are done with dA / dB
+        self.s_out.wait_stream(cur)
+        with torch.cuda.stream(self.s_in):
+            self.dB.copy_(self.hB, non_blocking=True)
+            for c in range(n):
+                sl = slice(c * rows, (c + 1) * rows)
+                self.dA[sl].copy_(self.hA[sl], non_blocking=True)
+                self.ev_in[c].record(self.s_in)
+        for c in range(n):
+            sl = slice(c * rows, (c + 1) * rows)
+            cur.wait_event(self.ev_in[c])
+            self.ctx.tk.gemm_rs(self.dA[sl], self.dB, self.out[sl], self.ctx.view)
+            self.ev_mm[c].record(cur)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(self.ev_mm[c])
+                self.hO[sl].copy_(self.out[sl], non_blocking=True)
+        cur.wait_stream(self.s_out)       # the step ends when the last rows are back on the host
 
     def config(self, value):
         P = self.ctx.world
@@ -272,6 +306,8 @@ class AllReduce:
         import torch
         self.ctx = ctx
         ctx.make_heap(3 * 129 + 3 * 2 + 64)
+        # NVLS (in-switch reduction) when the system has NVLink multicast: a collective opt-in
+        self.nvls = ctx.world > 1 and os.environ.get("DK_BENCH_NVLS", "1") != "0" and ctx.enable_multicast()
         g = torch.Generator(device="cuda").manual_seed(100 + ctx.rank)
         self.bufs = {}
         for name, shape in (("decode", (64, 8192)), ("prefill", (8192, 8192))):
@@ -299,7 +335,7 @@ class AllReduce:
         worst = 0.0
         for name in ("decode", "prefill"):
             xs, o = self.bufs[name]
-            for algo in ((0, 1) if ctx.world > 1 else (0,)):
+            for algo in (((0, 1, 2) if self.nvls else (0, 1)) if ctx.world > 1 else (0,)):
                 o.zero_()
                 ctx.barrier()
                 ctx.tk.allreduce(xs[0], o, ctx.view, algo)
@@ -317,8 +353,8 @@ class AllReduce:
         out = {}
         for name in ("decode", "prefill"):
             xs, o = self.bufs[name]
-            for algo, an in ((0, "oneshot"), (1, "twoshot")):
-                if self.ctx.world == 1 and algo == 1:
+            for algo, an in ((0, "oneshot"), (1, "twoshot"), (2, "nvls")):
+                if (self.ctx.world == 1 and algo >= 1) or (algo == 2 and not self.nvls):
                     continue
                 # called through the C ABI with prebuilt arguments: the Python entry point costs
                 # more host time per call than the 1 MiB kernel runs
@@ -346,7 +382,8 @@ class AllReduce:
     def config(self, value):
         c = {"workload": f"TP all-reduce bf16, 1 MiB [64x8192] + 128 MiB [8192x8192] per step, "
                          f"{self.ctx.world} GPU(s), algorithm picked by size",
-             "l2": "two input buffers alternated; the 128 MiB message exceeds L2"}
+             "l2": "two input buffers alternated; the 128 MiB message exceeds L2",
+             "nvls": bool(self.nvls)}
         c.update(self.detail)
         return c
 
@@ -525,6 +562,14 @@ class Ctx:
         assert self.iris.rank() == self.rank and self.iris.world_size() == self.world
         self.view = self.iris.get_device_view()
         self.dkview = self.capi.DkView.from_address(self.view._addr())
+
+    def enable_multicast(self):
+        """Collective: map the NVLink multicast object over the heaps; the view is refreshed."""
+        ok = bool(self.iris.enable_multicast())
+        if ok:
+            self.view = self.iris.get_device_view()
+            self.dkview = self.capi.DkView.from_address(self.view._addr())
+        return ok
 
     def barrier(self):
         self.torch.cuda.synchronize()

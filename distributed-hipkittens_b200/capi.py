@@ -66,6 +66,7 @@ def _declare(L: C.CDLL) -> None:
     L.dk_heap_free.argtypes = [vp, vp]
     L.dk_heap_barrier.argtypes = [vp]
     L.dk_heap_view.argtypes = [vp, C.POINTER(DkView)]
+    L.dk_heap_enable_multicast.argtypes = [vp]
     L.dk_heap_bytes_free.restype = sz
     L.dk_heap_bytes_free.argtypes = [vp]
     L.dk_comm_create.argtypes = [i, i, C.c_char_p, i, C.POINTER(vp)]
@@ -200,6 +201,14 @@ class Heap:
 
     def barrier(self) -> None:
         check(lib().dk_heap_barrier(self._h))
+
+    def enable_multicast(self) -> bool:
+        """Collective: map the NVLink multicast object over all ranks' heaps; False if unavailable."""
+        rc = lib().dk_heap_enable_multicast(self._h)
+        if rc == ERR_UNSUPPORTED:
+            return False
+        check(rc)
+        return True
 
     def view(self) -> DkView:
         v = DkView()

@@ -4,11 +4,18 @@
 // include/ or kernels/); this is the operation the named hot path adds, built on the same symmetric
 // heap and the same device-view convention as its GEMM (distributed-kernels/bf16_gemm/kernel.cpp:75).
 //
-// Two algorithms, both summing in fp32 in rank order so that every rank ends with identical bits:
+// Three algorithms. The first two sum in fp32 in rank order, so every rank ends with identical bits:
 //   one-shot  every rank reads all `world` inputs and writes the sum locally. (world-1) x S bytes
 //             come in over NVLink; one exchange. For small messages (decode).
 //   two-shot  rank r reduces slice r (reading the peers' slice r) and pushes the bf16 result into
 //             every rank's output. 2 (world-1)/world x S bytes per direction. For large messages.
+//
+//   NVLS      rank r reduces slice r with multimem.ld_reduce (the NVSwitch fetches the slice from
+//             every GPU and adds in fp32) and broadcasts the result with multimem.st (the switch
+//             writes it into every rank's output). About S bytes per direction per GPU, for every
+//             world size. Needs the heap's multicast mapping (dk_view.mc_base). The order of the
+//             switch's sum is not specified, but each element is reduced once and then broadcast,
+//             so all ranks still hold identical bits.
 //
 // Synchronisation is per block: block b of every rank handles the same elements, so block b only
 // has to meet the peers' block b. Flags live in the control block at the start of each rank's heap,
@@ -33,12 +40,14 @@ struct ARRank {
     const uint4* x[DK_MAX_RANKS];   // input of rank r as seen from this rank
     uint4* out[DK_MAX_RANKS];       // output of rank r as seen from this rank (two-shot pushes)
     unsigned* ctrl[DK_MAX_RANKS];   // control block of rank r
+    const uint4* mc_x;              // NVLS: input and output through the multicast mapping
+    uint4* mc_out;
     int rank;
 };
 struct ARJob {
     ARRank r[DK_MAX_RANKS];  // real launch: only r[0]; emulated launch: one per blockIdx.y
     int world;
-    int algo;                // 0 one-shot, 1 two-shot
+    int algo;                // 0 one-shot, 1 two-shot, 2 NVLS
     unsigned epoch;
     size_t nvec;             // 16-byte vectors (8 bf16) per rank input
     unsigned* status;
@@ -108,6 +117,20 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_kernel(const __grid_cons
                 if (r < world) add8(acc, v[r]);
             me.out[me.rank][i] = pack8(acc);
         }
+    } else if (job.algo == 2) {
+        const size_t slice = job.nvec / world;
+        const size_t lo = slice * me.rank;
+        size_t j = static_cast<size_t>(b) * AR_THREADS + threadIdx.x;
+        // four independent switch reductions in flight per thread
+        for (; j + 3 * stride < slice; j += 4 * stride) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = multimem_ld_reduce_add_bf16x8(me.mc_x + lo + j + u * stride);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) multimem_st_bf16x8(me.mc_out + lo + j + u * stride, v[u]);
+        }
+        for (; j < slice; j += stride)
+            multimem_st_bf16x8(me.mc_out + lo + j, multimem_ld_reduce_add_bf16x8(me.mc_x + lo + j));
     } else {
         const size_t slice = job.nvec / world;
         const size_t lo = slice * me.rank;
@@ -137,6 +160,12 @@ static size_t oneshot_max_bytes(int world) {
     return world <= 2 ? (4u << 20) : world <= 4 ? (1u << 20) : (512u << 10);
 }
 
+// Whether algo -1 may pick NVLS when the mapping exists (DK_ALLREDUCE_NVLS_AUTO=0 turns that off).
+static bool nvls_auto() {
+    const char* e = std::getenv("DK_ALLREDUCE_NVLS_AUTO");
+    return !(e && *e && std::atoi(e) == 0);
+}
+
 static int pick_blocks(size_t work_vecs, int sms, int ranks_in_launch) {
     size_t nb = (work_vecs + AR_THREADS * 4 - 1) / (AR_THREADS * 4);
     size_t cap = static_cast<size_t>(sms) * 2 / ranks_in_launch;  // 2 blocks of 512 threads per SM
@@ -146,15 +175,23 @@ static int pick_blocks(size_t work_vecs, int sms, int ranks_in_launch) {
     return static_cast<int>(nb);
 }
 
-static int resolve_algo(int algo, size_t n, int world, int* out) {
+// nvls_ok: the heap has a multicast mapping (real multi-GPU launches only).
+static int resolve_algo(int algo, size_t n, int world, bool nvls_ok, int* out) {
     DK_REQUIRE(algo >= -1 && algo <= 2, "algo must be -1 (auto), 0 (one-shot), 1 (two-shot) or 2 (NVLS)");
-    if (algo == 2) {
-        set_last_error("NVLS all-reduce needs a multicast mapping of the heap, which this build does not create");
-        return DK_ERR_UNSUPPORTED;
-    }
     const bool two_ok = (n % (static_cast<size_t>(8) * world)) == 0;
+    if (algo == 2) {
+        if (!nvls_ok) {
+            set_last_error("NVLS all-reduce needs the heap's NVLink multicast mapping, which this job does not "
+                           "have (no multicast support, DK_NVLS=0, or the set-up failed on some rank)");
+            return DK_ERR_UNSUPPORTED;
+        }
+        DK_REQUIRE(two_ok, "NVLS needs n to be a multiple of 8 * world elements");
+    }
     if (algo == 1) DK_REQUIRE(two_ok, "two-shot needs n to be a multiple of 8 * world elements");
-    if (algo == -1) algo = (two_ok && n * 2 > oneshot_max_bytes(world)) ? 1 : 0;
+    if (algo == -1) {
+        if (nvls_ok && two_ok && nvls_auto()) algo = 2;
+        else algo = (two_ok && n * 2 > oneshot_max_bytes(world)) ? 1 : 0;
+    }
     *out = algo;
     return DK_OK;
 }
@@ -178,9 +215,12 @@ extern "C" int dk_allreduce(const void* x, void* out, size_t n, int algo, const 
     DK_REQUIRE(view->heap != nullptr, "view has no heap handle");
     DK_REQUIRE(in_heap(view, x, n * 2), "the all-reduce input must lie inside the symmetric heap");
     int a = 0;
-    int rc = resolve_algo(algo, n, world, &a);
+    // auto may pick NVLS only if `out` can be written through the multicast mapping; an explicit
+    // request with `out` outside the heap is reported as such below
+    const bool mc = view->mc_base != nullptr;
+    int rc = resolve_algo(algo, n, world, algo == 2 ? mc : (mc && in_heap(view, out, n * 2)), &a);
     if (rc != DK_OK) return rc;
-    if (a == 1) DK_REQUIRE(in_heap(view, out, n * 2), "two-shot pushes into the peers' outputs: out must lie inside the symmetric heap");
+    if (a >= 1) DK_REQUIRE(in_heap(view, out, n * 2), "two-shot and NVLS write into the peers' outputs: out must lie inside the symmetric heap");
     if (a == 0) DK_REQUIRE(x != out, "one-shot cannot run in place: peers still read x while out is written");
 
     ARJob job{};
@@ -198,10 +238,16 @@ extern "C" int dk_allreduce(const void* x, void* out, size_t n, int algo, const 
         me.out[r] = a == 1 ? static_cast<uint4*>(peer_ptr(view, out, r)) : static_cast<uint4*>(out);
         me.ctrl[r] = ctrl_words(view, r);
     }
+    if (a == 2) {
+        const char* base = static_cast<const char*>(view->base[view->rank]);
+        char* mc = static_cast<char*>(view->mc_base);
+        me.mc_x = reinterpret_cast<const uint4*>(mc + (static_cast<const char*>(x) - base));
+        me.mc_out = reinterpret_cast<uint4*>(mc + (static_cast<const char*>(out) - base));
+    }
     int sms = 0;
     rc = sm_count(&sms);
     if (rc != DK_OK) return rc;
-    const int nb = pick_blocks(a == 1 ? job.nvec / world : job.nvec, sms, 1);
+    const int nb = pick_blocks(a >= 1 ? job.nvec / world : job.nvec, sms, 1);
     allreduce_kernel<<<dim3(nb, 1), AR_THREADS, 0, st>>>(job);
     DK_CUDA_OK(cudaGetLastError());
     return DK_OK;
@@ -216,7 +262,7 @@ extern "C" int dk_allreduce_all_ranks(int world, const dk_view* views, const voi
     DK_REQUIRE(n > 0 && n % 8 == 0, "n must be a positive multiple of 8 bf16 elements");
     DK_REQUIRE(epoch != 0, "epochs start at 1");
     int a = 0;
-    int rc = resolve_algo(algo, n, world, &a);
+    int rc = resolve_algo(algo, n, world, false, &a);  // ranks emulated on one GPU have no switch between them
     if (rc != DK_OK) return rc;
     ARJob job{};
     job.world = world;

@@ -14,8 +14,10 @@
 // over NVLink/NVSwitch by the memory system.
 #include "dk_heap.h"
 
+#include <fcntl.h>
 #include <unistd.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -26,13 +28,116 @@ int dk_comm_create(int, int, const char*, int, dk_comm**);
 int dk_comm_destroy(dk_comm*);
 int dk_comm_barrier(dk_comm*);
 int dk_comm_allgather_fd(dk_comm*, int, int*);
+int dk_comm_allgather(dk_comm*, const void*, size_t, void*);
 }
 
 namespace {
 
 size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// Take the multicast mapping down again (each step only if it was made).
+void multicast_teardown(dk_heap* h, const dk::DriverApi* api) {
+    if (h->mc_mapped) {
+        api->cuMemUnmap(h->mc_window, h->bytes);
+        h->mc_mapped = false;
+    }
+    if (h->mc_window) {
+        api->cuMemAddressFree(h->mc_window, h->bytes);
+        h->mc_window = 0;
+    }
+    if (h->mc_bound) {
+        api->cuMulticastUnbind(h->mc_handle, h->mc_dev, 0, h->bytes);
+        h->mc_bound = false;
+    }
+    if (h->mc_have) {
+        api->cuMemRelease(h->mc_handle);
+        h->mc_have = false;
+    }
+}
+
+// True when every rank reports `mine` (one all-gather; also a barrier).
+bool all_ranks_ok(dk_heap* h, bool mine) {
+    int v = mine ? 1 : 0;
+    int all[DK_MAX_RANKS] = {0};
+    if (dk_comm_allgather(h->comm, &v, sizeof(v), all) != DK_OK) return false;
+    for (int r = 0; r < h->world; ++r)
+        if (!all[r]) return false;
+    return true;
+}
+
+// DK_NVLS=1 makes dk_heap_create set the multicast mapping up by itself.
+bool multicast_at_create() {
+    const char* e = std::getenv("DK_NVLS");
+    return e && *e && std::atoi(e) == 1;
+}
+
+// One NVLink multicast object over all ranks' heaps: rank 0 creates it and hands its descriptor
+// round, every rank adds its device, then (all added) binds its own allocation at offset 0 and maps
+// the object. A store to mc_window + o then lands at offset o of EVERY rank's heap and a
+// multimem.ld_reduce there returns the sum over ranks, both performed by the switch. Every step
+// is agreed between the ranks, so a failure anywhere leaves all of them without the mapping
+// (dk_view.mc_base null) and the heap otherwise intact.
+void multicast_setup(dk_heap* h, const dk::DriverApi* api) {
+    bool ok = api->mc_ok && h->mc_gran != 0 && h->bytes % h->mc_gran == 0;
+    if (!all_ranks_ok(h, ok)) return;
+
+    CUmulticastObjectProp mp{};
+    mp.numDevices = static_cast<unsigned>(h->world);
+    mp.size = h->bytes;
+    mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+    int my_fd = -1;
+    if (h->rank == 0) {
+        ok = api->cuMulticastCreate(&h->mc_handle, &mp) == CUDA_SUCCESS;
+        h->mc_have = ok;
+        if (ok)
+            ok = api->cuMemExportToShareableHandle(&my_fd, h->mc_handle,
+                                                   CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0) == CUDA_SUCCESS;
+    }
+    if (my_fd < 0) my_fd = open("/dev/null", O_RDONLY);  // the exchange wants a descriptor from everyone
+    if (my_fd < 0) ok = false;
+    if (!all_ranks_ok(h, ok)) {
+        if (my_fd >= 0) close(my_fd);
+        multicast_teardown(h, api);
+        return;
+    }
+    int fds[DK_MAX_RANKS];
+    for (int& f : fds) f = -1;
+    ok = dk_comm_allgather_fd(h->comm, my_fd, fds) == DK_OK;
+    close(my_fd);
+    if (ok && h->rank != 0) {
+        ok = api->cuMemImportFromShareableHandle(&h->mc_handle,
+                                                 reinterpret_cast<void*>(static_cast<uintptr_t>(fds[0])),
+                                                 CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR) == CUDA_SUCCESS;
+        h->mc_have = ok;
+    }
+    for (int& f : fds)
+        if (f >= 0) close(f);
+    if (ok) ok = api->cuDeviceGet(&h->mc_dev, h->device) == CUDA_SUCCESS;
+    if (ok) ok = api->cuMulticastAddDevice(h->mc_handle, h->mc_dev) == CUDA_SUCCESS;
+    // memory may be bound only once ALL devices have been added: the agreement is the barrier
+    if (!all_ranks_ok(h, ok)) {
+        multicast_teardown(h, api);
+        return;
+    }
+    ok = api->cuMulticastBindMem(h->mc_handle, 0, h->handles[h->rank], 0, h->bytes, 0) == CUDA_SUCCESS;
+    h->mc_bound = ok;
+    if (ok) ok = api->cuMemAddressReserve(&h->mc_window, h->bytes, h->mc_gran, 0, 0) == CUDA_SUCCESS;
+    if (ok) {
+        ok = api->cuMemMap(h->mc_window, h->bytes, 0, h->mc_handle, 0) == CUDA_SUCCESS;
+        h->mc_mapped = ok;
+    }
+    if (ok) {
+        CUmemAccessDesc acc{};
+        acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+        acc.location.id = h->device;
+        acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+        ok = api->cuMemSetAccess(h->mc_window, h->bytes, &acc, 1) == CUDA_SUCCESS;
+    }
+    if (!all_ranks_ok(h, ok)) multicast_teardown(h, api);
+}
+
 int unmap_all(dk_heap* h, const dk::DriverApi* api) {
+    multicast_teardown(h, api);
     for (int r = 0; r < h->world; ++r) {
         if (h->mapped[r]) {
             api->cuMemUnmap(h->window + static_cast<size_t>(r) * h->bytes, h->bytes);
@@ -84,6 +189,28 @@ int dk_heap_create(size_t bytes, int rank, int world, const char* rendezvous, dk
         delete h;
         return DK_ERR_CUDA;
     }
+    // With NVLink multicast available the heap is also a whole number of multicast granules, so
+    // that it can be bound to a multicast object as one piece.
+    if (world > 1 && api->mc_ok) {
+        CUdevice cudev;
+        int supported = 0;
+        if (api->cuDeviceGet(&cudev, h->device) == CUDA_SUCCESS &&
+            api->cuDeviceGetAttribute(&supported, CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED, cudev) == CUDA_SUCCESS &&
+            supported) {
+            CUmulticastObjectProp mp{};
+            mp.numDevices = static_cast<unsigned>(world);
+            mp.size = round_up(bytes + DK_CTRL_BYTES, gran);
+            mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+            size_t g_rec = 0, g_min = 0;
+            if (api->cuMulticastGetGranularity(&g_min, &mp, CU_MULTICAST_GRANULARITY_MINIMUM) == CUDA_SUCCESS &&
+                api->cuMulticastGetGranularity(&g_rec, &mp, CU_MULTICAST_GRANULARITY_RECOMMENDED) == CUDA_SUCCESS &&
+                g_min != 0) {
+                // the recommended granule unless it would inflate small heaps beyond reason
+                h->mc_gran = (g_rec != 0 && g_rec <= (64u << 20)) ? g_rec : g_min;
+            }
+        }
+    }
+    if (h->mc_gran > gran) gran = round_up(h->mc_gran, gran);
     h->bytes = round_up(bytes + DK_CTRL_BYTES, gran);
 
     if (world > 1) {
@@ -167,6 +294,7 @@ int dk_heap_create(size_t bytes, int rank, int world, const char* rendezvous, dk
         return bail(DK_ERR_CUDA, "", CUDA_SUCCESS);
     }
     h->free_blocks[DK_CTRL_BYTES] = h->bytes - DK_CTRL_BYTES;
+    if (h->comm && multicast_at_create()) multicast_setup(h, api);
     if (h->comm) {
         rc = dk_comm_barrier(h->comm);
         if (rc != DK_OK) return bail(rc, "", CUDA_SUCCESS);
@@ -190,6 +318,30 @@ int dk_heap_destroy(dk_heap* h) {
     if (h->comm) dk_comm_destroy(h->comm);
     cudaSetDevice(prev);
     delete h;
+    return DK_OK;
+}
+
+int dk_heap_enable_multicast(dk_heap* h) {
+    using namespace dk;
+    DK_REQUIRE(h != nullptr, "heap is null");
+    if (h->mc_mapped) return DK_OK;
+    if (h->comm == nullptr) {
+        set_last_error("NVLink multicast needs a job of at least two ranks");
+        return DK_ERR_UNSUPPORTED;
+    }
+    const DriverApi* api;
+    int rc = driver_api(&api);
+    if (rc != DK_OK) return rc;
+    int prev = 0;
+    DK_CUDA_OK(cudaGetDevice(&prev));
+    DK_CUDA_OK(cudaSetDevice(h->device));
+    multicast_setup(h, api);
+    cudaSetDevice(prev);
+    if (!h->mc_mapped) {
+        set_last_error("NVLink multicast mapping not available (no multicast support on some rank, or a set-up "
+                       "step failed there); the heap works without it");
+        return DK_ERR_UNSUPPORTED;
+    }
     return DK_OK;
 }
 
@@ -266,7 +418,7 @@ int dk_heap_view(dk_heap* h, dk_view* out) {
     for (int r = 0; r < h->world; ++r)
         out->base[r] = reinterpret_cast<void*>(h->window + static_cast<size_t>(r) * h->bytes);
     out->heap_bytes = h->bytes;
-    out->mc_base = nullptr;
+    out->mc_base = h->mc_mapped ? reinterpret_cast<void*>(h->mc_window) : nullptr;
     out->heap = h;
     return DK_OK;
 }

@@ -28,6 +28,12 @@ struct dk_heap {
     CUmemGenericAllocationHandle handles[DK_MAX_RANKS] = {};
     bool have[DK_MAX_RANKS] = {};    // handles[r] holds a reference
     bool mapped[DK_MAX_RANKS] = {};  // rank r's segment is mapped into the window
+    // NVLink multicast object over all ranks' heaps (NVLS); zero when not set up
+    CUmemGenericAllocationHandle mc_handle = 0;
+    bool mc_have = false, mc_bound = false, mc_mapped = false;
+    CUdevice mc_dev = 0;
+    size_t mc_gran = 0;         // multicast granule the heap size was rounded to (0: no multicast)
+    CUdeviceptr mc_window = 0;  // `bytes` of address space: offset o = offset o of EVERY rank's heap
     dk_comm* comm = nullptr;
     unsigned epoch = 0;
     std::mutex mu;

@@ -46,6 +46,15 @@ int driver_api(const DriverApi** api) {
         ok = ok && resolve("cuMemImportFromShareableHandle", &g_api.cuMemImportFromShareableHandle);
         g_api.ok = ok;
         g_api_rc = ok ? DK_OK : DK_ERR_CUDA;
+        bool mc = ok;
+        mc = mc && resolve("cuDeviceGet", &g_api.cuDeviceGet);
+        mc = mc && resolve("cuDeviceGetAttribute", &g_api.cuDeviceGetAttribute);
+        mc = mc && resolve("cuMulticastCreate", &g_api.cuMulticastCreate);
+        mc = mc && resolve("cuMulticastAddDevice", &g_api.cuMulticastAddDevice);
+        mc = mc && resolve("cuMulticastBindMem", &g_api.cuMulticastBindMem);
+        mc = mc && resolve("cuMulticastUnbind", &g_api.cuMulticastUnbind);
+        mc = mc && resolve("cuMulticastGetGranularity", &g_api.cuMulticastGetGranularity);
+        g_api.mc_ok = mc;
     });
     *api = &g_api;
     return g_api_rc;

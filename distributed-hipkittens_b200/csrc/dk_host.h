@@ -63,6 +63,17 @@ struct DriverApi {
                                              unsigned long long) = nullptr;
     CUresult (*cuMemImportFromShareableHandle)(CUmemGenericAllocationHandle*, void*,
                                                CUmemAllocationHandleType) = nullptr;
+    // NVLink multicast objects (NVLS). Optional: mc_ok is false when the driver lacks them.
+    bool mc_ok = false;
+    CUresult (*cuDeviceGet)(CUdevice*, int) = nullptr;
+    CUresult (*cuDeviceGetAttribute)(int*, CUdevice_attribute, CUdevice) = nullptr;
+    CUresult (*cuMulticastCreate)(CUmemGenericAllocationHandle*, const CUmulticastObjectProp*) = nullptr;
+    CUresult (*cuMulticastAddDevice)(CUmemGenericAllocationHandle, CUdevice) = nullptr;
+    CUresult (*cuMulticastBindMem)(CUmemGenericAllocationHandle, size_t, CUmemGenericAllocationHandle,
+                                   size_t, size_t, unsigned long long) = nullptr;
+    CUresult (*cuMulticastUnbind)(CUmemGenericAllocationHandle, CUdevice, size_t, size_t) = nullptr;
+    CUresult (*cuMulticastGetGranularity)(size_t*, const CUmulticastObjectProp*,
+                                          CUmulticastGranularity_flags) = nullptr;
 };
 // Returns DK_OK and fills *api, or DK_ERR_CUDA when no driver is present.
 int driver_api(const DriverApi** api);

@@ -385,6 +385,24 @@ __device__ __forceinline__ unsigned signal_load_acquire_sys(const unsigned* p) {
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+// NVLink multicast (NVLS). `mc` is an address inside a mapping of a multicast object: the switch
+// performs the access on the same offset of every bound GPU's memory.
+// Sum over all GPUs of 8 bf16 values, accumulated in fp32 inside the switch, returned as bf16.
+__device__ __forceinline__ uint4 multimem_ld_reduce_add_bf16x8(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc)
+                 : "memory");
+    return v;
+}
+// Store 16 bytes to the same offset of every GPU's memory.
+__device__ __forceinline__ void multimem_st_bf16x8(void* mc, const uint4& v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x),
+                 "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
 // Bounded wait until *p >= target (wrap-safe). Returns false on timeout.
 __device__ __forceinline__ bool signal_wait_ge(const unsigned* p, unsigned target,
                                                const WaitCtx& w, unsigned site,

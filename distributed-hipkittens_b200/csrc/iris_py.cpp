@@ -149,6 +149,15 @@ public:
         return dv;
     }
 
+    // Collective: map the NVLink multicast object over all ranks' heaps. False when unavailable.
+    bool enable_multicast() {
+        const int rc = dk_heap_enable_multicast(heap_->h);
+        if (rc == DK_OK) return true;
+        if (rc == DK_ERR_UNSUPPORTED) return false;
+        throw_on(rc, "enable_multicast");
+        return false;
+    }
+
     uintptr_t heap_handle() const { return reinterpret_cast<uintptr_t>(heap_->h); }
 };
 
@@ -177,6 +186,9 @@ PYBIND11_MODULE(iris_py, m) {
              "    IrisTensor: Iris tensor object")
         .def("barrier", &IrisInstance::barrier, "Synchronize the device, then all ranks")
         .def("get_device_view", &IrisInstance::get_device_view, "Get device view for kernel usage")
+        .def("enable_multicast", &IrisInstance::enable_multicast,
+             "Collective over all ranks: map the NVLink multicast object over the heaps (NVLS all-reduce).\n"
+             "Returns False when the system has no multicast support. Not in the reference.")
         .def("_heap", &IrisInstance::heap_handle, "dk_heap* as an integer");
 
     py::class_<IrisTensor, std::shared_ptr<IrisTensor>>(m, "Tensor")

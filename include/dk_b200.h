@@ -95,6 +95,18 @@ int dk_heap_free(dk_heap* h, void* p);
 /* Host barrier across ranks (after cudaDeviceSynchronize of the caller's choice). */
 int dk_heap_barrier(dk_heap* h);
 int dk_heap_view(dk_heap* h, dk_view* out);
+/*
+ * Collective over all ranks of the heap: create one NVLink multicast object (NVLS) over the ranks'
+ * heaps and map it (cuMulticastCreate / AddDevice / BindMem + cuMemMap). Afterwards dk_view.mc_base
+ * is non-null: a multimem store to mc_base + o lands at offset o of EVERY rank's heap and a
+ * multimem.ld_reduce there returns the sum over ranks, both done by the NVSwitch. Every step is
+ * agreed between the ranks: on DK_ERR_UNSUPPORTED (no multicast support, or a step failed on some
+ * rank) no rank has the mapping and the heap works as before. DK_NVLS=1 in the environment makes
+ * dk_heap_create do this by itself. Opt-in because a process that dies while its memory is bound
+ * to a multicast object can disturb its peers' GPUs; dk_heap_destroy unbinds in order.
+ * No reference counterpart (iris has no multicast path at its call sites).
+ */
+int dk_heap_enable_multicast(dk_heap* h);
 /* Bytes still free (largest bump region), for tests. */
 size_t dk_heap_bytes_free(dk_heap* h);
 
@@ -174,8 +186,12 @@ int dk_moe_gemm_debug_counters(long long* device_buffer);
  * offset on every rank. algo: -1 auto by message size (DK_ALLREDUCE_ONESHOT_MAX_BYTES overrides
  * the crossover), 0 one-shot (every rank reads all inputs; out may be any local buffer, not x),
  * 1 two-shot (reduce a slice, push it to every rank; out must lie inside the heap, may alias x;
- * n % (8*world) == 0), 2 NVLS (DK_ERR_UNSUPPORTED: this build maps no multicast object).
- * world == 1 copies x to out. The reference has no counterpart: it contains no collective.
+ * n % (8*world) == 0), 2 NVLS (rank r reduces slice r inside the NVSwitch with multimem.ld_reduce
+ * and broadcasts it with multimem.st; same conditions as two-shot, plus the heap's multicast
+ * mapping, see dk_heap_enable_multicast, else DK_ERR_UNSUPPORTED; the switch's summation order is
+ * unspecified but every element is reduced once and broadcast, so ranks still agree bit for bit).
+ * Auto picks NVLS whenever the mapping exists and the conditions hold (DK_ALLREDUCE_NVLS_AUTO=0
+ * keeps auto to the first two). world == 1 copies x to out. The reference has no counterpart: it contains no collective.
  */
 int dk_allreduce(const void* x, void* out, size_t n, int algo, const dk_view* view, void* stream);
 /*

@@ -127,3 +127,79 @@ def test_peer_memory_path(world):
             assert results[r][f"allreduce{algo}"] <= 1e-2
             # every rank holds the same bits
             assert results[r][f"allreduce{algo}_sum"] == results[0][f"allreduce{algo}_sum"]
+
+
+def _nvls_worker(rank, world, job, q):
+    """NVLS all-reduce (multimem.ld_reduce + multimem.st through the NVSwitch). The heap leaves
+    through its destructor on every path, so the multicast binding is always undone in order."""
+    iris = None
+    res = {}
+    try:
+        os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), DK_JOB_ID=job)
+        sys.path.insert(0, str(ROOT))
+        sys.path.insert(0, str(ROOT / "distributed-hipkittens_b200"))
+        import iris_py
+        import tk_kernel
+        from oracle import dk_oracle as orc
+        torch.cuda.set_device(rank)
+        iris = iris_py.Iris(heap_size_mb=96)
+        res["nvls"] = bool(iris.enable_multicast())
+        if res["nvls"]:
+            view = iris.get_device_view()
+            for name, shape in (("small", (64, 8192)), ("large", (2048, 8192))):
+                xs = orc.make_allreduce_inputs(shape, world)
+                ref = orc.allreduce_ref(xs)
+                x = torch.as_tensor(iris.empty(list(shape)), device="cuda").view(torch.bfloat16)
+                o = torch.as_tensor(iris.empty(list(shape)), device="cuda").view(torch.bfloat16)
+                for it, algo in enumerate((2, 2, -1)):
+                    x.copy_(xs[rank])
+                    o.fill_(float("nan"))
+                    iris.barrier()
+                    tk_kernel.allreduce(x, o, view, algo)
+                    torch.cuda.synchronize()
+                    res[f"{name}{it}"] = orc.rel_fro(o.float().cpu(), ref)
+                    res[f"{name}{it}_sum"] = int(o.view(torch.int16).to(torch.int64).sum().item())
+                # in place
+                x.copy_(xs[rank])
+                iris.barrier()
+                tk_kernel.allreduce(x, x, view, 2)
+                torch.cuda.synchronize()
+                res[f"{name}_inplace"] = orc.rel_fro(x.float().cpu(), ref)
+                del x, o
+            res["status"] = tk_kernel.device_status()
+            del view
+        iris.barrier()
+    except Exception:
+        import traceback
+        res["error"] = traceback.format_exc()
+    finally:
+        q.put((rank, res))
+        del iris
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_nvls_allreduce(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    job = f"pytestnvls{os.getpid()}w{world}"
+    ps = [ctx.Process(target=_nvls_worker, args=(r, world, job, q)) for r in range(world)]
+    for p in ps:
+        p.start()
+    results = dict(q.get(timeout=240) for _ in ps)
+    for p in ps:
+        p.join(60)
+    for r in range(world):
+        assert "error" not in results[r], results[r].get("error")
+    if not results[0]["nvls"]:
+        assert not any(results[r]["nvls"] for r in range(world))   # the ranks agree
+        pytest.skip("no NVLink multicast support on this system")
+    for r in range(world):
+        assert results[r]["status"][0] == 0
+        for name in ("small", "large"):
+            for it in range(3):
+                assert results[r][f"{name}{it}"] <= 1e-2
+                assert results[r][f"{name}{it}_sum"] == results[0][f"{name}{it}_sum"]
+            assert results[r][f"{name}_inplace"] <= 1e-2
