@@ -167,6 +167,11 @@ static bool nvls_auto() {
 }
 
 static int pick_blocks(size_t work_vecs, int sms, int ranks_in_launch) {
+    // DK_ALLREDUCE_BLOCKS pins the grid (tuning; every rank must use the same value)
+    if (const char* e = std::getenv("DK_ALLREDUCE_BLOCKS")) {
+        const int v = std::atoi(e);
+        if (v >= 1 && v <= AR_MAX_BLOCKS) return v;
+    }
     size_t nb = (work_vecs + AR_THREADS * 4 - 1) / (AR_THREADS * 4);
     size_t cap = static_cast<size_t>(sms) * 2 / ranks_in_launch;  // 2 blocks of 512 threads per SM
     if (cap > AR_MAX_BLOCKS) cap = AR_MAX_BLOCKS;
