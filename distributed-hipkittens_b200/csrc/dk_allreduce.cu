@@ -166,14 +166,20 @@ static bool nvls_auto() {
     return !(e && *e && std::atoi(e) == 0);
 }
 
-static int pick_blocks(size_t work_vecs, int sms, int ranks_in_launch) {
+// Grid size, as measured on B200s: one 16-byte vector per thread while the message is small (a
+// 1 MiB message on 2 GPUs takes 14 us with 128 blocks against 20 us with 32), at most two blocks
+// per SM for the peer-load algorithms. NVLS saturates the switch with few requesters and slows
+// down with more (8 GPUs, 128 MiB: 294 us with 16 blocks, 301 with 64, 347 with 296; 16 MiB: 49 us
+// with 16 blocks, 59 with 64), so it gets at most 16 blocks (32 below four ranks).
+static int pick_blocks(size_t work_vecs, int sms, int ranks_in_launch, int algo, int world) {
     // DK_ALLREDUCE_BLOCKS pins the grid (tuning; every rank must use the same value)
     if (const char* e = std::getenv("DK_ALLREDUCE_BLOCKS")) {
         const int v = std::atoi(e);
         if (v >= 1 && v <= AR_MAX_BLOCKS) return v;
     }
-    size_t nb = (work_vecs + AR_THREADS * 4 - 1) / (AR_THREADS * 4);
-    size_t cap = static_cast<size_t>(sms) * 2 / ranks_in_launch;  // 2 blocks of 512 threads per SM
+    const size_t per_block = algo == 2 ? AR_THREADS * 4 : AR_THREADS;
+    size_t nb = (work_vecs + per_block - 1) / per_block;
+    size_t cap = algo == 2 ? (world >= 4 ? 16 : 32) : static_cast<size_t>(sms) * 2 / ranks_in_launch;
     if (cap > AR_MAX_BLOCKS) cap = AR_MAX_BLOCKS;
     if (nb > cap) nb = cap;
     if (nb < 1) nb = 1;
@@ -194,7 +200,10 @@ static int resolve_algo(int algo, size_t n, int world, bool nvls_ok, int* out) {
     }
     if (algo == 1) DK_REQUIRE(two_ok, "two-shot needs n to be a multiple of 8 * world elements");
     if (algo == -1) {
-        if (nvls_ok && two_ok && nvls_auto()) algo = 2;
+        // With four or more ranks NVLS moves the fewest bytes and measured fastest at every size
+        // (8 GPUs: 1 MiB 14.7 us against 17.9 two-shot, 128 MiB 294 us against 370). With two
+        // ranks it moves 1.5x the bytes of two-shot and is never the better choice.
+        if (nvls_ok && two_ok && world >= 4 && nvls_auto()) algo = 2;
         else algo = (two_ok && n * 2 > oneshot_max_bytes(world)) ? 1 : 0;
     }
     *out = algo;
@@ -252,7 +261,7 @@ extern "C" int dk_allreduce(const void* x, void* out, size_t n, int algo, const 
     int sms = 0;
     rc = sm_count(&sms);
     if (rc != DK_OK) return rc;
-    const int nb = pick_blocks(a >= 1 ? job.nvec / world : job.nvec, sms, 1);
+    const int nb = pick_blocks(a >= 1 ? job.nvec / world : job.nvec, sms, 1, a, world);
     allreduce_kernel<<<dim3(nb, 1), AR_THREADS, 0, st>>>(job);
     DK_CUDA_OK(cudaGetLastError());
     return DK_OK;
@@ -292,7 +301,7 @@ extern "C" int dk_allreduce_all_ranks(int world, const dk_view* views, const voi
     int sms = 0;
     rc = sm_count(&sms);
     if (rc != DK_OK) return rc;
-    const int nb = pick_blocks(a == 1 ? job.nvec / world : job.nvec, sms, world);
+    const int nb = pick_blocks(a == 1 ? job.nvec / world : job.nvec, sms, world, a, world);
     // all ranks' blocks wait for one another: they must be co-resident, hence a cooperative launch
     void* args[] = {&job};
     DK_CUDA_OK(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(allreduce_kernel), dim3(nb, world),

@@ -190,8 +190,8 @@ int dk_moe_gemm_debug_counters(long long* device_buffer);
  * and broadcasts it with multimem.st; same conditions as two-shot, plus the heap's multicast
  * mapping, see dk_heap_enable_multicast, else DK_ERR_UNSUPPORTED; the switch's summation order is
  * unspecified but every element is reduced once and broadcast, so ranks still agree bit for bit).
- * Auto picks NVLS whenever the mapping exists and the conditions hold (DK_ALLREDUCE_NVLS_AUTO=0
- * keeps auto to the first two). world == 1 copies x to out. The reference has no counterpart: it contains no collective.
+ * Auto picks NVLS when the mapping exists, the conditions hold and world >= 4, where it measured
+ * fastest at every size (DK_ALLREDUCE_NVLS_AUTO=0 keeps auto to the first two). world == 1 copies x to out. The reference has no counterpart: it contains no collective.
  */
 int dk_allreduce(const void* x, void* out, size_t n, int algo, const dk_view* view, void* stream);
 /*
