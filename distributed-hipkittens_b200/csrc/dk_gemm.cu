@@ -23,8 +23,9 @@
 // of the partial product is written, as bf16, into slot [rank] of the staging area of the rank
 // that OWNS those rows (peer memory, over NVLink) as sixteen contiguous 4 KiB bulk copies (the
 // staging area is tile-major, so a peer write never has to be scattered over rows), followed by
-// a release store of the call number into that tile's flag [rank] at the owner. Row-tiles are visited starting with the rows
-// of rank+1 and ending with this rank's own, so every link is busy from the first tile on.
+// a release store of the call number into that tile's flag [rank] at the owner. Tiles are visited
+// with the owners rotating fastest (rank+1, rank+2, ..., this rank), see tile_coords: every link is
+// busy all the time and the partials of a tile arrive at its owner at about the same time.
 //   warps 6-11  reducers: for every tile of this rank's own rows that this CTA computes, wait
 //               (bounded) for the `world` flags, sum the `world` bf16 partials in fp32 in rank order
 //               and write bf16, while the MMA warp is already working on the next tile.
@@ -71,8 +72,8 @@ struct GemmArgs {
     int tiles_m, tiles_n, num_kb;
     int world, rank;
     int rows_per_rank;  // rows of the output owned by one rank (M when world == 1)
-    int m_tile_rot;     // first row-tile visited
-    int group_m;        // row-tiles per raster group
+    int tiles_per_owner;  // reduce-scatter: row-tiles (of 128 * PAIR rows) per owner; 0 = one rank
+    int group_m;          // row-tiles per raster group (reduce-scatter: per owner)
     int epi_mode;       // 0 direct stores, 1 TMA stores
     int phases;         // bit 0: GEMM tiles, bit 1: reduce this rank's rows
     __nv_bfloat16* dst[DK_MAX_RANKS];  // per owner: where this rank's partial (or C) goes
@@ -95,9 +96,32 @@ enum : unsigned {
     SITE_RS_FLAG = 6
 };
 
-// t -> (m, n) in units of the launch's tiles (tiles_m counts tiles of 128 * PAIR rows)
+// t -> (m, n) in units of the launch's tiles (tiles_m counts tiles of 128 * PAIR rows).
+// One rank: grouped raster, group_m row-tiles x all column tiles, rows fastest.
+// Reduce-scatter (tiles_per_owner > 0): inside a group, owners rotate fastest: the tiles with the
+// same position (row-tile inside the owner's rows, column tile) are computed for owner rank+1,
+// rank+2, ..., and last for this rank itself, before the position advances. All ranks walk the
+// positions in the same order, so the `world` partials of an output tile are produced at about the
+// same time everywhere: each tile can be reduced right after it was computed, while its staged
+// partials are still in L2, and the reduction work is spread over the whole kernel instead of
+// piling up behind a last phase of own tiles. group_m * world row-tiles are live at a time.
 __device__ __forceinline__ void tile_coords(int t, const GemmArgs& g, int& m, int& n) {
     const int group_m = g.group_m;
+    if (g.tiles_per_owner > 0) {
+        const int per_group = group_m * g.world * g.tiles_n;
+        const int grp = t / per_group;
+        const int first = grp * group_m;
+        const int gsz = min(g.tiles_per_owner - first, group_m);
+        const int r = t - grp * per_group;
+        const int span = gsz * g.world;
+        n = r / span;
+        const int w = r - n * span;
+        const int m_in = w / g.world;
+        int owner = g.rank + 1 + (w - m_in * g.world);
+        if (owner >= g.world) owner -= g.world;
+        m = owner * g.tiles_per_owner + first + m_in;
+        return;
+    }
     const int per_group = group_m * g.tiles_n;
     const int grp = t / per_group;
     const int first_m = grp * group_m;
@@ -105,8 +129,6 @@ __device__ __forceinline__ void tile_coords(int t, const GemmArgs& g, int& m, in
     const int r = t - grp * per_group;
     m = first_m + r % gsz;
     n = r / gsz;
-    m += g.m_tile_rot;
-    if (m >= g.tiles_m) m -= g.tiles_m;
 }
 
 // Epilogue warps call this once the bulk stores of a tile have completed (each warp's issuing lane
@@ -623,7 +645,7 @@ int gemm_bf16_impl(const void* A, const void* Bt, void* C, int M, int N, int K, 
     g.world = 1;
     g.rank = 0;
     g.rows_per_rank = g.tiles_m * pair * BM;  // one owner
-    g.m_tile_rot = 0;
+    g.tiles_per_owner = 0;
     g.epi_mode = epilogue < 0 ? 1 : epilogue;
     g.phases = 1;
     g.dst[0] = static_cast<__nv_bfloat16*>(C);
@@ -690,13 +712,15 @@ int gemm_rs_impl(const void* A, const void* Bt, void* out, int M, int N, int Klo
     g.N = N;
     g.K = Kloc;
     g.tiles_m = M / BM / pair;   // tiles of 128 * pair rows
-    g.group_m = group_m_setting() / pair;
+    // world * group_m row-tiles are live at a time: keep that near the one-rank group size
+    g.group_m = group_m_setting() / pair / world;
+    if (g.group_m < 1) g.group_m = 1;
     g.tiles_n = (N + BN - 1) / BN;
     g.num_kb = (Kloc + BK - 1) / BK;
     g.world = world;
     g.rank = rank;
     g.rows_per_rank = mloc;
-    g.m_tile_rot = ((rank + 1) % world) * (mloc / BM / pair);
+    g.tiles_per_owner = mloc / BM / pair;
     // Pushes to peers always use TMA bulk stores: with direct 16-byte stores to peer memory an
     // 8-GPU run stalled until its peer waits ran out, so that variant is not offered across GPUs.
     (void)epilogue;
