@@ -73,6 +73,7 @@ struct GemmArgs {
     int world, rank;
     int rows_per_rank;  // rows of the output owned by one rank (M when world == 1)
     int tiles_per_owner;  // reduce-scatter: row-tiles (of 128 * PAIR rows) per owner; 0 = one rank
+    int m_tile_rot;       // phased order only: first row-tile visited
     int group_m;          // row-tiles per raster group (reduce-scatter: per owner)
     int epi_mode;       // 0 direct stores, 1 TMA stores
     int phases;         // bit 0: GEMM tiles, bit 1: reduce this rank's rows
@@ -129,6 +130,10 @@ __device__ __forceinline__ void tile_coords(int t, const GemmArgs& g, int& m, in
     const int r = t - grp * per_group;
     m = first_m + r % gsz;
     n = r / gsz;
+    // phased reduce-scatter order (DK_GEMM_RS_ORDER=phased): all tiles of owner rank+1 first,
+    // ..., this rank's own rows last
+    m += g.m_tile_rot;
+    if (m >= g.tiles_m) m -= g.tiles_m;
 }
 
 // Epilogue warps call this once the bulk stores of a tile have completed (each warp's issuing lane
@@ -646,6 +651,7 @@ int gemm_bf16_impl(const void* A, const void* Bt, void* C, int M, int N, int K, 
     g.rank = 0;
     g.rows_per_rank = g.tiles_m * pair * BM;  // one owner
     g.tiles_per_owner = 0;
+    g.m_tile_rot = 0;
     g.epi_mode = epilogue < 0 ? 1 : epilogue;
     g.phases = 1;
     g.dst[0] = static_cast<__nv_bfloat16*>(C);
@@ -712,15 +718,18 @@ int gemm_rs_impl(const void* A, const void* Bt, void* out, int M, int N, int Klo
     g.N = N;
     g.K = Kloc;
     g.tiles_m = M / BM / pair;   // tiles of 128 * pair rows
-    // world * group_m row-tiles are live at a time: keep that near the one-rank group size
-    g.group_m = group_m_setting() / pair / world;
+    const char* order = std::getenv("DK_GEMM_RS_ORDER");
+    const bool phased = order != nullptr && std::string(order) == "phased";
+    // interleaved: world * group_m row-tiles are live at a time; keep that near the one-rank group
+    g.group_m = phased ? group_m_setting() / pair : group_m_setting() / pair / world;
     if (g.group_m < 1) g.group_m = 1;
     g.tiles_n = (N + BN - 1) / BN;
     g.num_kb = (Kloc + BK - 1) / BK;
     g.world = world;
     g.rank = rank;
     g.rows_per_rank = mloc;
-    g.tiles_per_owner = mloc / BM / pair;
+    g.tiles_per_owner = phased ? 0 : mloc / BM / pair;
+    g.m_tile_rot = phased ? ((rank + 1) % world) * (mloc / BM / pair) : 0;
     // Pushes to peers always use TMA bulk stores: with direct 16-byte stores to peer memory an
     // 8-GPU run stalled until its peer waits ran out, so that variant is not offered across GPUs.
     (void)epilogue;
