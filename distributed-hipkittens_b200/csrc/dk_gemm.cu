@@ -8,16 +8,23 @@
 // through iris.store to its own rank. This kernel keeps the contract (same operand layouts, same
 // CTA tile footprint) and nothing of the mechanism:
 //
-//   warp 0      TMA producer: cp.async.bulk.tensor loads of A (128x64) and Bt (256x64) tiles,
-//               128-byte swizzle, into a 4-stage shared-memory ring, completion on mbarriers
-//   warp 1      MMA issuer: one thread issues tcgen05.mma (128x256x16, kind::f16) reading the ring
-//               through shared-memory descriptors, accumulating into one of two 256-column TMEM
-//               buffers; tcgen05.commit frees ring stages and publishes finished accumulators
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of A (128x64) and Bt tiles, 128-byte swizzle,
+//               into a shared-memory ring, completion on mbarriers
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (kind::f16, K = 16 per instruction) reading
+//               the ring through shared-memory descriptors, accumulating into one of two
+//               256-column TMEM buffers; tcgen05.commit frees ring stages and publishes finished
+//               accumulators
 //   warps 2-5   epilogue: tcgen05.ld (lane quarter = warp % 4), fp32 -> bf16, then either 16-byte
 //               global stores or swizzled shared-memory staging + TMA bulk stores
 //
-// Persistent: one CTA per SM walks a static tile list in a grouped raster (16 row-tiles per group)
-// so that concurrently running CTAs share A and Bt tiles in L2.
+// Two instantiations. PAIR = 2 (default where M and the rows per rank are multiples of 256): a
+// cluster of two CTAs computes a 256x256 tile with tcgen05.mma.cta_group::2 issued by the leader;
+// each CTA stages its 128 rows of A and half of the Bt tile (32 KiB stages, six deep), and both
+// CTAs' loads complete on the leader's mbarrier. PAIR = 1: one CTA per 128x256 tile, 48 KiB stages,
+// four deep.
+//
+// Persistent: one CTA per SM walks a static tile list in a grouped raster (2048 rows per group) so
+// that concurrently running CTAs share A and Bt tiles in L2.
 //
 // Reduce-scatter mode (world > 1): A and Bt hold this rank's K-shard. Each finished 128x256 tile
 // of the partial product is written, as bf16, into slot [rank] of the staging area of the rank
