@@ -94,6 +94,23 @@ void dispatch_micro(py::object A, py::object B, py::object C, py::object view, i
     throw_on(dk_gemm_bf16(a.ptr, b.ptr, c.ptr, M_local, N, K, v, -1, current_stream()), "dispatch_micro");
 }
 
+// The single-GPU form of the reference's GEMM module: dispatch_micro(A[M,K], Bt[N,K], C[M,N])
+// (kernels/cdna4/gemm/bf16fp32/256_256_64_32_with16x32.cpp:329-339, called that way by its
+// test.py:28 and bench.py:34). M, N, K come from the tensors, as there (g.M, g.N, g.K are the
+// globals' runtime dimensions).
+void dispatch_micro3(py::object A, py::object Bt, py::object C) {
+    TensorArg a = tensor_arg(A, "torch.bfloat16");
+    TensorArg b = tensor_arg(Bt, "torch.bfloat16");
+    TensorArg c = tensor_arg(C, "torch.bfloat16");
+    if (a.shape.size() != 2 || b.shape.size() != 2 || c.shape.size() != 2)
+        throw std::runtime_error("dispatch_micro expects 2-D tensors A[M,K], Bt[N,K], C[M,N]");
+    const int M = static_cast<int>(a.shape[0]), K = static_cast<int>(a.shape[1]);
+    const int N = static_cast<int>(b.shape[0]);
+    if (b.shape[1] != K) throw std::runtime_error("A and Bt disagree on K");
+    if (c.shape[0] != M || c.shape[1] != N) throw std::runtime_error("C must be [M, N]");
+    throw_on(dk_gemm_bf16(a.ptr, b.ptr, c.ptr, M, N, K, nullptr, -1, current_stream()), "dispatch_micro");
+}
+
 // One reduce-scatter workspace per (heap, M, N), allocated from the heap on first use. Every rank
 // makes the same calls in the same order, so the offsets agree.
 std::map<std::tuple<uintptr_t, int, int>, void*> g_rs_workspaces;
@@ -267,6 +284,8 @@ PYBIND11_MODULE(tk_kernel, m) {
     m.def("dispatch_micro", &dispatch_micro,
           "C[M_local,N] = A[M_local,K] @ B[N,K]^T (bf16, fp32 accumulate). Positional arguments: "
           "A, B, C, iris_view, M_local, N, K, row_offset");
+    m.def("dispatch_micro", &dispatch_micro3,
+          "C[M,N] = A[M,K] @ Bt[N,K]^T (bf16, fp32 accumulate), the single-GPU form. Positional: A, Bt, C");
     m.def("gemm_rs", &gemm_rs,
           "Out[M/P,N] = reduce-scatter over ranks of A[M,K/P] @ Bt[N,K/P]^T. Positional: A, Bt, Out, view");
     m.def("allreduce", &allreduce, py::arg("X"), py::arg("Out"), py::arg("view"), py::arg("algo") = -1,

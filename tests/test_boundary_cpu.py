@@ -74,6 +74,11 @@ def test_dispatch_micro_argument_errors():
         tk_kernel.dispatch_micro(torch.zeros(4, 4).t()[:, :2], 0, 0, None, 2, 2, 2, 0)
     with pytest.raises(TypeError):
         tk_kernel.dispatch_micro(torch.zeros(2, 2))  # positional arity is part of the contract
+    # the single-GPU three-argument form (kernels/cdna4/gemm/bf16fp32/256_256_64_32_with16x32.cpp:335-339)
+    with pytest.raises(RuntimeError, match="Expected a torch.Tensor"):
+        tk_kernel.dispatch_micro(1, 2, 3)
+    with pytest.raises(RuntimeError, match="Tensor must be on CUDA device"):
+        tk_kernel.dispatch_micro(torch.zeros(2, 2), torch.zeros(2, 2), torch.zeros(2, 2))
 
 
 def test_product_path_has_no_cpu_fallback(capi):

@@ -86,6 +86,33 @@ def test_gemm_argument_errors(capi):
         capi.gemm_bf16(torch.zeros(16, 64, device="cuda"), torch.zeros(16, 64, device="cuda"))
 
 
+# (m, n, k) of the reference's single-GPU script kernels/cdna4/gemm/bf16fp32/test.py:6-14
+REFERENCE_TEST_SHAPES = [(8192, 8192, 8192), (4096, 8192, 2048), (8192, 4096, 2048), (8192, 2048, 4096),
+                         (512, 1024, 1024), (512, 1024, 2048), (2048, 1024, 512)]
+
+
+@pytest.mark.parametrize("m,n,k", REFERENCE_TEST_SHAPES)
+def test_dispatch_micro_three_argument_form(orc, m, n, k):
+    """tk_kernel.dispatch_micro(A, Bt, C) as the reference's test.py:22-31 calls it: unscaled randn
+    operands (seed 0), Bt = B.t().contiguous(), checked with its criterion
+    (allclose(rtol=1e-2): elements whose value nearly cancels cannot meet a purely relative bound
+    in bf16, so the share of elements inside it is asserted) and with the oracle's norm."""
+    import tk_kernel
+    g = torch.Generator().manual_seed(0)
+    A = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    B = torch.randn(k, n, generator=g).to(torch.bfloat16)
+    Bt = B.t().contiguous()
+    C = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    tk_kernel.dispatch_micro(A.cuda(), Bt.cuda(), C)
+    torch.cuda.synchronize()
+    assert tk_kernel.device_status()[0] == 0
+    ref = orc.gemm_ref(A, Bt)
+    got = C.float().cpu()
+    assert orc.rel_fro(got, ref) <= TOL
+    inside = torch.isclose(got, ref, rtol=1e-2, atol=1e-8).float().mean().item()
+    assert inside >= 0.995, inside
+
+
 def test_dispatch_micro_reference_call(orc):
     """The reference's call, argument for argument (distributed-kernels/bf16_gemm/example.py:110-121)."""
     import iris_py
