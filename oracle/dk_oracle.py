@@ -302,3 +302,62 @@ def make_moe_inputs(T: int, H: int, F: int, E: int, k: int, seed: int = 0, zipf_
         w2q.append(q); w2s.append(s)
     return (x, logits.contiguous(), torch.stack(w13q), torch.stack(w13s), torch.stack(w2q),
             torch.stack(w2s))
+
+
+# --------------------------------------------------------------------------- MXFP8 (1x32 e8m0 blocks)
+# The block-scaled format the reference ships and tests: e4m3 elements with one e8m0 (power of
+# two) scale per 32 consecutive elements of K. Follows the host code of its fixtures:
+# compute_e8m0 and the quantisation loop at tests/unit/cdna4/warp/register/tile/mma_scaled.cu:200-232
+# (the same code is at kernels/cdna4/gemm/mxfp8/MXFP8_8wave/8_wave_NT.cu:286-327), the CPU
+# expectation at mma_scaled.cu:234-247, the per-iteration scale packing at mma_scaled.cu:249-264.
+# Pinned by tests/golden/mx_fixture.npz, regenerated from that fixture's seed and distribution
+# (std::mt19937(123), N(0, 0.5)) by tests/golden/make_mx_golden.cpp.
+MX_BLOCK = 32
+
+
+def mx_quant(x: torch.Tensor):
+    """x fp32 [R, K], K % 32 == 0 -> (q e4m3 bytes as uint8 [R, K], s e8m0 as uint8 [R, K/32]).
+    s = clamp(floor(log2(amax)) + 127, 0, 254), 0 for an all-zero block; q = e4m3(x * 2^(127-s)):
+    the block maximum lands in [1, 2)."""
+    R, K = x.shape
+    assert K % MX_BLOCK == 0
+    xb = x.float().reshape(R, K // MX_BLOCK, MX_BLOCK)
+    amax = xb.abs().amax(dim=-1)
+    # floor(log2(.)) of an fp32 value is its unbiased exponent (frexp gives amax = m * 2^e, m in [0.5, 1))
+    e = torch.frexp(amax)[1].to(torch.int32) - 1
+    s = torch.where(amax == 0, torch.zeros_like(e), (e + 127).clamp(0, 254))
+    inv = torch.ldexp(torch.ones_like(amax), (127 - s).to(torch.int32))
+    q = (xb * inv[..., None]).reshape(R, K).to(torch.float8_e4m3fn).view(torch.uint8)
+    return q, s.to(torch.uint8)
+
+
+def mx_dequant(q_u8: torch.Tensor, s_u8: torch.Tensor) -> torch.Tensor:
+    R, K = q_u8.shape
+    f = torch.ldexp(torch.ones(R, K // MX_BLOCK), s_u8.to(torch.int32) - 127)
+    return (q_u8.view(torch.float8_e4m3fn).float().reshape(R, K // MX_BLOCK, MX_BLOCK) * f[..., None]).reshape(R, K)
+
+
+def mx_gemm_ref(aq, sa, bq, sb) -> torch.Tensor:
+    """C[M, N] = dequant(A) @ dequant(B)^T in fp32 (products of e4m3 values and powers of two are
+    exact in fp32; only the order of the fp32 additions differs between implementations)."""
+    return mx_dequant(aq, sa) @ mx_dequant(bq, sb).t()
+
+
+def mx_pack_iter(s_u8: torch.Tensor) -> torch.Tensor:
+    """The reference's device layout of the scales: per K iteration of 128 elements one uint32 per
+    row holding its four e8m0 bytes, little endian: [K/128, R] (mma_scaled.cu:249-264)."""
+    R, SK = s_u8.shape
+    assert SK % 4 == 0
+    b = s_u8.reshape(R, SK // 4, 4).to(torch.int64)
+    w = b[..., 0] | (b[..., 1] << 8) | (b[..., 2] << 16) | (b[..., 3] << 24)
+    return w.t().contiguous().to(torch.int64)
+
+
+def mx_sf_atoms(s_u8: torch.Tensor) -> torch.Tensor:
+    """The layout the sm_100 tensor core wants the scales in (one 512-byte atom per 128 rows x 128
+    elements of K, byte offset r0*16 + r1*4 + k for row r0 + 32*r1 and 32-element group k), which a
+    32x128b.warpx4 tcgen05.cp moves to four tensor-memory columns: [R/128, K/128, 32, 4, 4] bytes."""
+    R, SK = s_u8.shape
+    assert R % 128 == 0 and SK % 4 == 0
+    t = s_u8.reshape(R // 128, 4, 32, SK // 4, 4)          # [rb, r1, r0, kb, k]
+    return t.permute(0, 3, 2, 1, 4).contiguous()            # [rb, kb, r0, r1, k]

@@ -215,3 +215,50 @@ def test_c_e4m3_conversion_exhaustive_against_torch():
     assert bool((s == 1.0).all())
     want = x.float().to(torch.float8_e4m3fn).view(torch.uint8)
     assert torch.equal(q, want)
+
+
+# ---- MXFP8 (1x32 e8m0) oracle against the reference's regenerated fixture -----------------------
+def test_mx_oracle_matches_reference_fixture(orc):
+    """tests/golden/mx_fixture.npz: the reference's mma_scaled fixture (mt19937(123), N(0, 0.5),
+    256^3) regenerated by make_mx_golden.cpp. The Python oracle must reproduce its quantisation bit
+    for bit and its CPU expectation to fp32 summation-order accuracy; the fixture's own acceptance
+    (|err| <= 0.1 % of max|c|, mma_scaled.cu:296-307) is asserted as well."""
+    fx = np.load(GOLD / "mx_fixture.npz")
+    a, b = torch.from_numpy(fx["a"]), torch.from_numpy(fx["b"])
+    aq, sa = orc.mx_quant(a)
+    bq, sb = orc.mx_quant(b)
+    assert np.array_equal(sa.numpy(), fx["sa"]) and np.array_equal(sb.numpy(), fx["sb"])
+    assert np.array_equal(aq.numpy(), fx["aq"]) and np.array_equal(bq.numpy(), fx["bq"])
+    # the block maximum lands in [1, 2) before rounding: no element can saturate
+    assert float(aq.view(torch.float8_e4m3fn).float().abs().max()) <= 2.0
+    c = orc.mx_gemm_ref(aq, sa, bq, sb)
+    want = torch.from_numpy(fx["c"])
+    c_max = float(want.abs().max())
+    assert float((c - want).abs().max()) <= 1e-5 * c_max
+    assert float((c - want).abs().max()) <= 1e-3 * c_max          # the fixture's acceptance
+    # quantisation error itself, against the unquantised product: a few per cent (3 mantissa bits)
+    assert orc.rel_fro(c, a @ b.t()) < 0.06
+
+
+def test_mx_scale_layouts(orc):
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(256, 512, generator=g) * torch.logspace(-6, 6, 512)[None, :]
+    x[5, 64:96] = 0                                     # an all-zero block: scale byte 0
+    q, s = orc.mx_quant(x)
+    assert s.shape == (256, 16) and int(s[5, 2]) == 0
+    assert torch.equal(q[5, 64:96], torch.zeros(32, dtype=torch.uint8))
+    # dequantised values stay within one e4m3 step (2^-3 relative, 2^-4 after rounding) of x
+    d = orc.mx_dequant(q, s)
+    blk_max = x.reshape(256, 16, 32).abs().amax(-1, keepdim=True).expand(-1, -1, 32).reshape(256, 512)
+    assert bool(((d - x).abs() <= blk_max * 2.0 ** -4 + 1e-30).all())
+    # the reference's per-iteration packing: byte j of word [ki, row] is the scale of block 4*ki + j
+    w = orc.mx_pack_iter(s)
+    assert w.shape == (4, 256)
+    for ki, row, j in ((0, 0, 0), (1, 7, 3), (3, 255, 2)):
+        assert (int(w[ki, row]) >> (8 * j)) & 0xFF == int(s[row, 4 * ki + j])
+    # the tensor-core atom layout: row r0 + 32*r1 of row block rb, group k of K block kb
+    t = orc.mx_sf_atoms(s)
+    assert t.shape == (2, 4, 32, 4, 4)
+    for rb, kb, r0, r1, k in ((0, 0, 0, 0, 0), (1, 3, 31, 3, 3), (0, 2, 17, 1, 2)):
+        assert int(t[rb, kb, r0, r1, k]) == int(s[rb * 128 + r1 * 32 + r0, kb * 4 + k])
+    assert t.flatten()[((1 * 4 + 3) * 32 + 31) * 16 + 3 * 4 + 3] == s[255, 15]   # byte offset r0*16 + r1*4 + k
