@@ -146,6 +146,11 @@ def cpu_reference_tflops(budget_s: float = 15.0):
                          f"(oracle gemm_ref, torch CPU fp32)"), dt
 
 
+def gemm_rs_workload_name(P):
+    return (f"gemm_rs M={M_TOK} N={N_OUT} K={K_FULL} K-sharded over {P} GPU(s), "
+            f"out rows reduce-scattered (Llama-70B MLP down-proj shape)")
+
+
 def run_reference(args, rank, out):
     """--impl reference: the reference's CPU implementation of the path, rank 0 only."""
     if rank != 0:
@@ -163,7 +168,8 @@ def run_reference(args, rank, out):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": f"gemm_rs M={M_TOK} N={N_OUT} K={K_FULL} (bounded CPU sample per step)"},
+        # the same workload string as the GPU arm prints for this N; what a step sampled is in cpu_baseline
+        "config": {"workload": gemm_rs_workload_name(args.gpus)},
         "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": desc},
         "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -274,8 +280,7 @@ class GemmRs:
 
     def config(self, value):
         P = self.ctx.world
-        return {"workload": f"gemm_rs M={M_TOK} N={N_OUT} K={K_FULL} K-sharded over {P} GPU(s), "
-                            f"out rows reduce-scattered (Llama-70B MLP down-proj shape)",
+        return {"workload": gemm_rs_workload_name(P),
                 "l2": f"{self.nsets} operand sets of {self.shard_bytes / 1e6:.0f} MB rotated: "
                       f"{(self.nsets - 1) * self.shard_bytes / 1e6:.0f} MB of other operands pass between two "
                       f"uses of a set (L2 is 126 MB)",
