@@ -199,6 +199,32 @@ def quant_block128(x: torch.Tensor):
     return q.reshape(R, Cc).view(torch.uint8), s.contiguous()
 
 
+def quant_block128_pow2(x: torch.Tensor):
+    """The same block quantiser with the scale rounded UP to a power of two (what an e8m0 scale can
+    hold): s = 2^ceil(log2(amax/448)), 1 for an all-zero block. The block maximum then lands in
+    (224, 448], so no element saturates and at most one bit of the e4m3 range is given up.
+    Returns (q uint8 [R,C], s fp32 [R/128, C/128], e8m0 uint8 [R/128, C/128] = log2(s) + 127).
+    A definition of this build (the reference has no 128x128 quantiser); it exists so that the
+    tensor core can apply block scales itself."""
+    R, Cc = x.shape
+    assert R % BLOCK == 0 and Cc % BLOCK == 0
+    xf = x.float().reshape(R // BLOCK, BLOCK, Cc // BLOCK, BLOCK)
+    amax = xf.abs().amax(dim=(1, 3))
+    m, e = torch.frexp(amax / FP8_MAX)                       # amax/448 = m * 2^e, m in [0.5, 1)
+    e = torch.where(m == 0.5, e - 1, e).to(torch.int32)      # exact powers of two stay as they are
+    e = torch.where(amax > 0, e, torch.zeros_like(e)).clamp(-127, 127)
+    s = torch.ldexp(torch.ones_like(amax), e)
+    q = (xf / s[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return q.reshape(R, Cc).view(torch.uint8), s.contiguous(), (e + 127).to(torch.uint8)
+
+
+def block128_scales_to_sf_atoms(e8m0: torch.Tensor) -> torch.Tensor:
+    """128x128 power-of-two block scales as the tensor core's 1x32 scale atoms (see mx_sf_atoms):
+    every row of a block and each of its four 32-element K groups carries the block's byte.
+    [R/128, C/128] -> [R/128, C/128, 32, 4, 4]."""
+    return e8m0[:, :, None, None, None].expand(-1, -1, 32, 4, 4).contiguous()
+
+
 def dequant_block128(q_u8: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
     R, Cc = q_u8.shape
     qf = q_u8.view(torch.float8_e4m3fn).float().reshape(R // BLOCK, BLOCK, Cc // BLOCK, BLOCK)

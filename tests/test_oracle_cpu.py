@@ -262,3 +262,33 @@ def test_mx_scale_layouts(orc):
     for rb, kb, r0, r1, k in ((0, 0, 0, 0, 0), (1, 3, 31, 3, 3), (0, 2, 17, 1, 2)):
         assert int(t[rb, kb, r0, r1, k]) == int(s[rb * 128 + r1 * 32 + r0, kb * 4 + k])
     assert t.flatten()[((1 * 4 + 3) * 32 + 31) * 16 + 3 * 4 + 3] == s[255, 15]   # byte offset r0*16 + r1*4 + k
+
+
+def test_pow2_block_quantiser(orc):
+    """Power-of-two 128x128 scales: never saturate, give up at most one bit against the fp32
+    scale, and are the same numbers whether read as fp32 scales or as e8m0 bytes in 1x32 atoms."""
+    g = torch.Generator().manual_seed(11)
+    x = (torch.randn(256, 384, generator=g) * torch.logspace(-3, 3, 384)[None, :]).to(torch.bfloat16)
+    x[:128, :128] = 0
+    x[128:, 128:256] = 448.0 * 2.0 ** -5               # amax/448 an exact power of two
+    q, s, e = orc.quant_block128_pow2(x)
+    q0, s0 = orc.quant_block128(x)
+    assert float(s[0, 0]) == 1.0 and int(e[0, 0]) == 127
+    assert float(s[1, 1]) == 2.0 ** -5 and int(e[1, 1]) == 122
+    assert bool((s >= s0).all()) and bool((s < 2 * s0 + 1e-30).all())      # rounded up, by less than 2x
+    assert torch.equal(torch.ldexp(torch.ones_like(s), e.to(torch.int32) - 127), s)
+    qf = q.view(torch.float8_e4m3fn).float()
+    assert float(qf.abs().max()) <= 448.0
+    blk_max = qf.abs().reshape(2, 128, 3, 128).amax(dim=(1, 3))
+    assert bool((blk_max[s0 != 1] > 223.0).all())                            # block maximum in (224, 448]
+    # dequantised error: the fp32-scale quantiser's bound doubled at worst
+    d, d0 = orc.dequant_block128(q, s), orc.dequant_block128(q0, s0)
+    xf = x.float()
+    assert orc.rel_fro(d, xf) <= 2.0 * orc.rel_fro(d0, xf) + 1e-6
+    # as scale atoms for the tensor core: 16 identical bytes per row group
+    atoms = orc.block128_scales_to_sf_atoms(e)
+    assert atoms.shape == (2, 3, 32, 4, 4) and bool((atoms[1, 1] == 122).all())
+    # and those atoms describe the same dequantisation as the 1x32 format would
+    s_rows = e[:, :, None].expand(-1, -1, 4).reshape(2, 12).repeat_interleave(128, dim=0)   # [R, C/32]
+    assert torch.allclose(orc.mx_dequant(q, s_rows), d)
+    assert torch.equal(orc.mx_sf_atoms(s_rows), atoms)
