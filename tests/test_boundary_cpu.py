@@ -94,6 +94,23 @@ def test_product_path_has_no_cpu_fallback(capi):
         iris_py.Iris(16)
 
 
+def test_argument_errors_need_no_gpu(capi):
+    """Argument checks come before any CUDA call, so they answer the same with or without a GPU."""
+    L = capi.lib()
+    assert L.dk_heap_enable_multicast(None) == capi.ERR_ARG
+    assert b"heap is null" in L.dk_last_error_string()
+    assert L.dk_gemm_pair_mode(7) == capi.ERR_ARG
+    assert L.dk_gemm_pair_mode(1) == 0
+    L.dk_gemm_rs_workspace_bytes.restype = C.c_size_t
+    assert L.dk_gemm_rs_workspace_bytes(8192, 8192, 1) == 0
+    # 2 parities x 8 slots x 1024 rows x 8192 columns x 2 bytes of staging + 2 x 256 tiles x 8 flags
+    assert L.dk_gemm_rs_workspace_bytes(8192, 8192, 8) == 2 * 8 * 1024 * 8192 * 2 + 2 * 256 * 8 * 4
+    assert L.dk_gemm_rs_workspace_bytes(8192, 8192, 9) == 0          # more ranks than supported
+    assert L.dk_allreduce(None, None, 8, -1, None, None) == capi.ERR_ARG
+    assert L.dk_set_peer_wait_ms(0) == capi.ERR_ARG
+    assert L.dk_set_peer_wait_ms(20000) == 0
+
+
 # ---- host bootstrap between two processes (no GPU involved) -----------------------------------
 def _comm_worker(rank, world, name, q):
     import sys
