@@ -125,6 +125,14 @@ def cpu_reference_tflops(budget_s: float = 15.0):
     with all host threads. Returns (TFLOP/s, threads, description, seconds)."""
     import torch
     from oracle import dk_oracle as orc
+    # all the host threads this process may use: torchrun exports OMP_NUM_THREADS=1 to every rank,
+    # which would time a one-thread baseline when the reference arm runs under it
+    try:
+        avail = len(os.sched_getaffinity(0))
+    except AttributeError:
+        avail = os.cpu_count() or 1
+    if torch.get_num_threads() < avail:
+        torch.set_num_threads(avail)
     threads = torch.get_num_threads()
     g = torch.Generator().manual_seed(0)
     Bt = (torch.randn(N_OUT, K_FULL, generator=g) / math.sqrt(K_FULL)).to(torch.bfloat16)

@@ -105,3 +105,31 @@ def test_two_ranks_gloo():
     assert out[0]["recv_rows"] + out[1]["recv_rows"] == 64 * world * 2
     rc4, dt, msg = out[0]["after_leave"]
     assert rc4 == 4 and dt < 5.0 and "barrier" in msg     # DK_ERR_BOOTSTRAP, not a hang
+
+
+def test_reference_arm_under_torchrun_prints_one_line_from_rank0():
+    """bench.py --impl reference launched like the GPU arm (torchrun, 2 ranks): rank 0 alone times
+    the CPU path, with all the host threads it may use although torchrun exports OMP_NUM_THREADS=1,
+    and prints ONE JSON line; the other rank exits 0 without work."""
+    import json
+    import subprocess
+    port = 29900 + os.getpid() % 90
+    env = dict(os.environ)
+    env.pop("OMP_NUM_THREADS", None)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", str(port), str(ROOT / "bench.py"),
+                        "--impl", "reference", "--gpus", "2", "--steps", "1", "--warmup", "0"],
+                       capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [ln for ln in r.stdout.splitlines() if ln.strip()]
+    assert len(lines) == 1, r.stdout
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["n_gpus"] == 2 and d["metric"] == "gemm_rs_tflops"
+    assert d["cpu_baseline"]["kind"] == "port" and d["gpu_launches"] == 0
+    assert d["e2e"]["value"] == d["value"] and d["e2e"]["h2d_bytes_per_step"] == 0
+    try:
+        avail = len(os.sched_getaffinity(0))
+    except AttributeError:
+        avail = os.cpu_count() or 1
+    assert d["cpu_baseline"]["cores"] == avail
+    assert "K-sharded over 2 GPU(s)" in d["config"]["workload"]
