@@ -94,6 +94,12 @@ def _declare(L: C.CDLL) -> None:
     L.dk_moe_permute_static.argtypes = [vp, i, i, i, i, i, vp, vp, i, vp, vp, vp]
     L.dk_moe_combine.argtypes = [vp, vp, vp, i, i, i, vp, vp]
     L.dk_moe_grouped_gemm_fp8.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, vp, vp, vp]
+    L.dk_mx_sf_bytes.restype = sz
+    L.dk_mx_sf_bytes.argtypes = [i, i]
+    L.dk_mx_quant.argtypes = [vp, i, i, i, vp, vp, vp, vp]
+    L.dk_gemm_mxfp8.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, vp]
+    L.dk_quant_block128_pow2.argtypes = [vp, i, i, vp, i, i, vp, vp, vp, vp, vp]
+    L.dk_moe_grouped_gemm_mxfp8.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, vp, vp, vp, vp]
     L.dk_peer_barrier.argtypes = [C.POINTER(DkView), vp]
     L.dk_peer_barrier_epoch.argtypes = [C.POINTER(DkView), C.c_uint, vp]
     L.dk_set_peer_wait_ms.argtypes = [i]
@@ -374,6 +380,84 @@ def moe_ffn_fp8(xq, xs, w13q, w13s, w2q, w2s, offsets, stream=None):
     """gate/up grouped GEMM + SiLU*mul + requantise, then the down grouped GEMM. Returns Y bf16 [R,H]."""
     hq, hs = moe_grouped_gemm_fp8(xq, xs, w13q, w13s, offsets, True, stream)
     return moe_grouped_gemm_fp8(hq, hs, w2q, w2s, offsets, False, stream)
+
+
+# ---------------------------------------------------------------------------- MXFP8
+def mx_quant(x, stream=None):
+    """x [R, K] bf16 or fp32 -> (q e4m3 bytes [R, K], s e8m0 bytes [R, K/32], scale atoms
+    [ceil(R/128), K/128, 512] in the layout the tensor core reads)."""
+    import torch
+    _need_cuda(x)
+    if x.dtype not in (torch.bfloat16, torch.float32):
+        raise RuntimeError("mx_quant expects bfloat16 or float32")
+    R, K = x.shape
+    q = torch.empty((R, K), dtype=torch.uint8, device=x.device)
+    s = torch.empty((R, K // 32), dtype=torch.uint8, device=x.device)
+    atoms = torch.empty(((R + 127) // 128, K // 128, 512), dtype=torch.uint8, device=x.device)
+    check(lib().dk_mx_quant(_ptr(x), 1 if x.dtype == torch.float32 else 0, R, K, _ptr(q), _ptr(s), _ptr(atoms),
+                            _stream_ptr(stream)))
+    return q, s, atoms
+
+
+def gemm_mxfp8(aq, sfa, bq, sfb, out_dtype=None, stream=None):
+    """C[M, N] = dequant(A) @ dequant(B)^T from e4m3 bytes and scale atoms; bf16 (default) or fp32 out."""
+    import torch
+    _need_cuda(aq, sfa, bq, sfb)
+    M, K = aq.shape
+    N = bq.shape[0]
+    f32 = out_dtype == torch.float32
+    out = torch.empty((M, N), dtype=torch.float32 if f32 else torch.bfloat16, device=aq.device)
+    check(lib().dk_gemm_mxfp8(_ptr(aq), _ptr(sfa), _ptr(bq), _ptr(sfb), _ptr(out), M, N, K, 1 if f32 else 0,
+                              _stream_ptr(stream)))
+    return out
+
+
+def quant_block128_pow2(x, rows: int | None = None, row_map=None, map_mode: int = 0, k: int = 1, stream=None):
+    """(q uint8 [R,C], s fp32 [R/128,C/128], e8 uint8 [R/128,C/128], atoms uint8 [R/128,C/128,512]):
+    128x128 block quantisation with power-of-two scales."""
+    import torch
+    _need_cuda(x)
+    if x.dtype != torch.bfloat16:
+        raise RuntimeError("quant_block128_pow2 expects bfloat16")
+    R = x.shape[0] if rows is None else rows
+    Cc = x.shape[1]
+    dev = x.device
+    q = torch.empty((R, Cc), dtype=torch.uint8, device=dev)
+    s = torch.empty((R // 128, Cc // 128), dtype=torch.float32, device=dev)
+    e8 = torch.empty((R // 128, Cc // 128), dtype=torch.uint8, device=dev)
+    atoms = torch.empty((R // 128, Cc // 128, 512), dtype=torch.uint8, device=dev)
+    check(lib().dk_quant_block128_pow2(_ptr(x), R, Cc, _ptr(row_map) if row_map is not None else None,
+                                       map_mode, k, _ptr(q), _ptr(s), _ptr(e8), _ptr(atoms), _stream_ptr(stream)))
+    return q, s, e8, atoms
+
+
+def moe_grouped_gemm_mxfp8(xq, x_atoms, wq, w_atoms, offsets, gated: bool, stream=None):
+    """Grouped GEMM on the block-scaled tensor-core path. gated: returns (hq uint8 [R,F], e8 uint8
+    [R/128,F/128], atoms [R/128,F/128,512]); else Y bf16 [R,N]. Rows beyond offsets[E] stay zero."""
+    import torch
+    _need_cuda(xq, x_atoms, wq, w_atoms, offsets)
+    R, K = xq.shape
+    E = wq.shape[0]
+    dev = xq.device
+    if gated:
+        N = wq.shape[1] // 2
+        out = torch.zeros((R, N), dtype=torch.uint8, device=dev)
+        e8 = torch.full((R // 128, N // 128), 127, dtype=torch.uint8, device=dev)
+        atoms = torch.full((R // 128, N // 128, 512), 127, dtype=torch.uint8, device=dev)
+        check(lib().dk_moe_grouped_gemm_mxfp8(_ptr(xq), _ptr(x_atoms), _ptr(wq), _ptr(w_atoms), _ptr(offsets), E,
+                                              R, N, K, 1, _ptr(out), _ptr(e8), _ptr(atoms), _stream_ptr(stream)))
+        return out, e8, atoms
+    N = wq.shape[1]
+    out = torch.zeros((R, N), dtype=torch.bfloat16, device=dev)
+    check(lib().dk_moe_grouped_gemm_mxfp8(_ptr(xq), _ptr(x_atoms), _ptr(wq), _ptr(w_atoms), _ptr(offsets), E, R,
+                                          N, K, 0, _ptr(out), None, None, _stream_ptr(stream)))
+    return out
+
+
+def moe_ffn_mxfp8(xq, x_atoms, w13q, w13_atoms, w2q, w2_atoms, offsets, stream=None):
+    """gate/up + SiLU*mul + requantise, then down, with power-of-two block scales. Y bf16 [R,H]."""
+    hq, _, h_atoms = moe_grouped_gemm_mxfp8(xq, x_atoms, w13q, w13_atoms, offsets, True, stream)
+    return moe_grouped_gemm_mxfp8(hq, h_atoms, w2q, w2_atoms, offsets, False, stream)
 
 
 # ---------------------------------------------------------------------------- expert parallel

@@ -228,6 +228,7 @@ extern "C" int dk_allreduce(const void* x, void* out, size_t n, int algo, const 
     DK_REQUIRE(world <= DK_MAX_RANKS && view->rank >= 0 && view->rank < world, "bad view");
     DK_REQUIRE(view->heap != nullptr, "view has no heap handle");
     DK_REQUIRE(in_heap(view, x, n * 2), "the all-reduce input must lie inside the symmetric heap");
+    if (const int pending = device_status_pending()) return pending;
     int a = 0;
     // auto may pick NVLS only if `out` can be written through the multicast mapping; an explicit
     // request with `out` outside the heap is reported as such below

@@ -709,6 +709,7 @@ int gemm_rs_impl(const void* A, const void* Bt, void* out, int M, int N, int Klo
     DK_REQUIRE(M % (world * BM) == 0, "M must be a multiple of world * 128");
     DK_REQUIRE(workspace != nullptr, "gemm_rs needs a workspace inside the symmetric heap");
     DK_REQUIRE(seq != 0, "sequence numbers start at 1");
+    if (const int pending = device_status_pending()) return pending;
     const int rank = view->rank;
     const int mloc = M / world;
     const size_t slot_elems = static_cast<size_t>(mloc) * ((N + BN - 1) / BN) * BN;
@@ -824,6 +825,8 @@ extern "C" int dk_gemm_rs(const void* A, const void* Bt, void* out, int M, int N
         DK_REQUIRE(h != nullptr, "view has no heap handle; use dk_gemm_rs_phase with explicit sequence numbers");
         DK_REQUIRE(workspace != nullptr && dk::in_heap(view, workspace, dk::gemm_rs_workspace_bytes(M, N, view->world)),
                    "workspace must lie inside the symmetric heap");
+        // before the call number advances: a refused call must not leave this rank one call ahead
+        if (const int pending = dk::device_status_pending()) return pending;
         std::lock_guard<std::mutex> lk(h->mu);
         auto it = h->rs_seq.find(workspace);
         DK_REQUIRE(it != h->rs_seq.end(), "workspace was not initialised with dk_gemm_rs_workspace_init");

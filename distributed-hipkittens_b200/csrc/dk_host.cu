@@ -129,6 +129,27 @@ int device_status_ptr(unsigned** dev_ptr) {
     return DK_OK;
 }
 
+int device_status_pending() {
+    int dev = 0;
+    DK_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return DK_OK;
+    unsigned code = 0, block = 0, site = 0, detail = 0;
+    {
+        std::lock_guard<std::mutex> lk(g_status_mu);
+        const volatile unsigned* h = g_status_host[dev];
+        if (h == nullptr || h[0] == 0u) return DK_OK;
+        code = h[0];
+        block = h[1];
+        site = h[2];
+        detail = h[3];
+    }
+    set_last_error("an earlier kernel on this device recorded an error (code " + std::to_string(code) +
+                   ", block " + std::to_string(block) + ", site " + std::to_string(site) + ", detail " +
+                   std::to_string(detail) + ") that has not been read with dk_last_device_status; "
+                   "nothing was launched");
+    return DK_ERR_DEVICE;
+}
+
 static int g_sm_count[64] = {0};
 int sm_count(int* out) {
     int dev = 0;
@@ -172,7 +193,7 @@ const char* dk_strerror(int code) {
         case DK_OK: return "ok";
         case DK_ERR_ARG: return "invalid argument";
         case DK_ERR_CUDA: return "CUDA call failed";
-        case DK_ERR_DEVICE: return "device-side wait timed out";
+        case DK_ERR_DEVICE: return "device-side error record pending (a bounded wait gave up, or a bad index was skipped)";
         case DK_ERR_BOOTSTRAP: return "rank rendezvous failed";
         case DK_ERR_NOMEM: return "symmetric heap exhausted";
         case DK_ERR_UNSUPPORTED: return "not supported on this device";

@@ -89,6 +89,11 @@ int make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t in
 
 // 4 words of host-mapped memory per device for the bounded-wait error record.
 int device_status_ptr(unsigned** dev_ptr);
+// DK_ERR_DEVICE while the current device holds an error record the host has not read yet with
+// dk_last_device_status (the record is left in place), DK_OK otherwise. Collectives call this before
+// they launch: with an unread record every later wait on a peer gives up at once, so their results
+// would be wrong without any other sign.
+int device_status_pending();
 
 int sm_count(int* out);
 

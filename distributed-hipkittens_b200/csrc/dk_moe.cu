@@ -183,10 +183,15 @@ __global__ void __launch_bounds__(PERM_CHUNK) moe_place_kernel(const int* __rest
 // t/16 + 16*i, i = 0..7. Source rows come straight from x, or through a row map:
 //   map_mode 0: row r of x;  1: row map[r] / k of x (gather), zeros where map[r] < 0;
 //   2: row r of x where map[r] >= 0, zeros elsewhere (rows already in place, padding undefined)
+// POW2: the scale is rounded UP to a power of two, s = 2^ceil(log2(amax/448)) (1 for an all-zero
+// block), and also written as an e8m0 byte (log2(s) + 127) and as the 512-byte scale atom the
+// block-scaled tensor-core path reads (the byte repeated for the block's 128 rows x 4 K groups).
+template <bool POW2>
 __global__ void __launch_bounds__(256) quant_block128_kernel(const __nv_bfloat16* __restrict__ x, int R, int C,
                                                              const int* __restrict__ map, int map_mode,
                                                              int k, uint8_t* __restrict__ q,
-                                                             float* __restrict__ s) {
+                                                             float* __restrict__ s, uint8_t* __restrict__ e8,
+                                                             uint8_t* __restrict__ atoms) {
     __shared__ float red[8];
     const int bc = blockIdx.x, br = blockIdx.y;
     const int cchunk = (threadIdx.x & 15) * 8;
@@ -221,8 +226,24 @@ __global__ void __launch_bounds__(256) quant_block128_kernel(const __nv_bfloat16
     amax = red[0];
 #pragma unroll
     for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
-    const float scale = amax > 0.f ? amax / 448.0f : 1.0f;
-    if (threadIdx.x == 0) s[static_cast<size_t>(br) * (C / 128) + bc] = scale;
+    float scale = amax > 0.f ? amax / 448.0f : 1.0f;
+    const size_t blk = static_cast<size_t>(br) * (C / 128) + bc;
+    if (POW2) {
+        int ex = 0;
+        if (amax > 0.f) {
+            const float m = frexpf(scale, &ex);  // amax/448 = m * 2^ex, m in [0.5, 1)
+            if (m == 0.5f) ex -= 1;              // exact powers of two stay as they are
+            ex = max(-127, min(127, ex));
+        }
+        scale = ldexpf(1.0f, ex);
+        const uint32_t b8 = static_cast<uint32_t>(ex + 127);
+        if (threadIdx.x < 32) {
+            const uint32_t rep = b8 * 0x01010101u;
+            reinterpret_cast<uint4*>(atoms + blk * 512)[threadIdx.x] = make_uint4(rep, rep, rep, rep);
+        }
+        if (threadIdx.x == 0 && e8 != nullptr) e8[blk] = static_cast<uint8_t>(b8);
+    }
+    if (threadIdx.x == 0 && s != nullptr) s[blk] = scale;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int r = br * 128 + r0 + 16 * i;
@@ -417,8 +438,26 @@ int dk_quant_block128(const void* x, int R, int C, const int* row_map, int map_m
     DK_REQUIRE(map_mode != 1 || k >= 1, "k must be positive");
     if (R == 0) return DK_OK;
     DK_REQUIRE(x && q && s, "null buffer");
-    quant_block128_kernel<<<dim3(C / 128, R / 128), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(x), R, C, row_map, map_mode, k, static_cast<uint8_t*>(q), s);
+    quant_block128_kernel<false><<<dim3(C / 128, R / 128), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x), R, C, row_map, map_mode, k, static_cast<uint8_t*>(q), s, nullptr,
+        nullptr);
+    DK_CUDA_OK(cudaGetLastError());
+    return DK_OK;
+}
+
+int dk_quant_block128_pow2(const void* x, int R, int C, const int* row_map, int map_mode, int k, void* q,
+                           float* s, void* e8, void* sf_atoms, void* stream) {
+    using namespace dk;
+    DK_REQUIRE(R >= 0 && C > 0 && R % 128 == 0 && C % 128 == 0, "R and C must be multiples of 128");
+    DK_REQUIRE(map_mode >= 0 && map_mode <= 2, "map_mode must be 0, 1 or 2");
+    DK_REQUIRE(map_mode == 0 || row_map != nullptr, "row_map is null");
+    DK_REQUIRE(map_mode != 1 || k >= 1, "k must be positive");
+    if (R == 0) return DK_OK;
+    DK_REQUIRE(x && q && sf_atoms, "null buffer");
+    DK_REQUIRE((reinterpret_cast<uintptr_t>(sf_atoms) & 15) == 0, "the scale atoms must be 16-byte aligned");
+    quant_block128_kernel<true><<<dim3(C / 128, R / 128), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x), R, C, row_map, map_mode, k, static_cast<uint8_t*>(q), s,
+        static_cast<uint8_t*>(e8), static_cast<uint8_t*>(sf_atoms));
     DK_CUDA_OK(cudaGetLastError());
     return DK_OK;
 }

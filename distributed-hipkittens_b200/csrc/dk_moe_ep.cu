@@ -129,6 +129,8 @@ __global__ void __launch_bounds__(256) moe_combine_ep_kernel(const CombineEpArgs
 static int launch_peer_barrier(const dk_view* view, cudaStream_t st, unsigned explicit_epoch = 0) {
     if (view == nullptr || view->world <= 1) return DK_OK;
     DK_REQUIRE(view->heap != nullptr || explicit_epoch != 0, "view has no heap handle");
+    // before the epoch advances: a refused call must not leave this rank one epoch ahead
+    if (const int pending = device_status_pending()) return pending;
     BarrierArgs a{};
     a.rank = view->rank;
     a.world = view->world;

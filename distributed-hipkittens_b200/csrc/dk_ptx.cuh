@@ -92,7 +92,9 @@ struct WaitCtx {
     unsigned long long peer_limit_ns = 20000000000ull;
 };
 
-enum : unsigned { DK_DEV_OK = 0, DK_DEV_TIMEOUT = 1, DK_DEV_PEER_TIMEOUT = 2 };
+// DK_DEV_BAD_INDEX: a kernel met an index from device memory (an expert id, a row, an offset) that
+// points outside the buffers it was given; it skipped the access and recorded {code, block, site, detail}.
+enum : unsigned { DK_DEV_OK = 0, DK_DEV_TIMEOUT = 1, DK_DEV_PEER_TIMEOUT = 2, DK_DEV_BAD_INDEX = 3 };
 
 static __device__ __noinline__ void record_timeout(const WaitCtx& w, unsigned code, unsigned site,
                                             unsigned detail) {
@@ -287,6 +289,67 @@ __device__ __forceinline__ void umma_f8(uint32_t d_tmem, uint64_t a_desc, uint64
             "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
             : "memory");
 }
+// ---- block-scaled MMA (kind::mxf8f6f4.block_scale): D (+)= (A * 2^(sfa-127)) * (B * 2^(sfb-127))^T
+// with one e8m0 scale byte per row and per 32 elements of K, read from tensor memory.
+//
+// Scale bytes reach tensor memory as 512-byte "atoms" covering 128 rows x 128 elements of K: byte
+// r0*16 + r1*4 + k is the scale of row r0 + 32*r1 for the 32-element group k. One
+// tcgen05.cp.32x128b.warpx4 moves an atom from shared memory into four consecutive 32-bit columns
+// (lane r0 of every lane quarter, column r1, byte k); the MMA picks byte k with the scale ids of
+// its instruction descriptor.
+//
+// Shared-memory descriptor of one atom: 32 rows of 16 bytes, no swizzle, K-major; 8-row core
+// matrices 128 bytes apart (stride byte offset), a single 16-byte column (leading offset unused).
+__device__ __forceinline__ uint64_t umma_desc_sf_atom(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4);
+    d |= static_cast<uint64_t>(128 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    return d;  // layout type 0: no swizzle
+}
+template <int CTAS>
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
+    if constexpr (CTAS == 1)
+        asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+    else
+        asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+// Instruction descriptor of the block-scaled kind: e4m3 x e4m3 (formats 0), both K-major, fp32
+// accumulate implied; N>>3 at bit 17, scale format e8m0 at bit 23, M>>4 at bit 24, the byte of the
+// scale columns to use at bits 4 (B) and 29 (A).
+__host__ __device__ constexpr uint32_t umma_idesc_mx(uint32_t m, uint32_t n, uint32_t sf_id) {
+    return (sf_id << 4) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24) | (sf_id << 29);
+}
+template <int CTAS>
+__device__ __forceinline__ void umma_mxf8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    if constexpr (CTAS == 1)
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "setp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+            "}\n" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+            : "memory");
+    else
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "setp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+            "}\n" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+            : "memory");
+}
+// Contiguous bulk copy global -> this CTA's shared memory (16-byte aligned, size a multiple of 16),
+// byte count completing on an mbarrier.
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
 // Make the mbarrier track completion of all tcgen05 operations this thread issued so far.
 // Implies tcgen05.fence::before_thread_sync.
 template <int CTAS>

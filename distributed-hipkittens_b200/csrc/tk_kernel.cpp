@@ -239,6 +239,84 @@ py::object moe_ffn_fp8(py::object Xq, py::object Xs, py::object W13q, py::object
     return y;
 }
 
+// ---- MXFP8 (1x32 e8m0 block scales) and the MoE path with power-of-two 128x128 scales
+py::tuple mx_quant(py::object X) {
+    TensorArg x = tensor_arg(X);
+    const bool f32 = x.dtype == "torch.float32";
+    if (!f32 && x.dtype != "torch.bfloat16") throw std::runtime_error("Expected dtype torch.bfloat16 or torch.float32, got " + x.dtype);
+    if (x.shape.size() != 2) throw std::runtime_error("X must be [R, K]");
+    const int R = static_cast<int>(x.shape[0]), K = static_cast<int>(x.shape[1]);
+    if (K % 128 != 0) throw std::runtime_error("K must be a multiple of 128");
+    py::object q = torch_empty({R, K}, "uint8", X);
+    py::object s = torch_empty({R, K / 32}, "uint8", X);
+    py::object atoms = torch_empty({(R + 127) / 128, K / 128, 512}, "uint8", X);
+    throw_on(dk_mx_quant(x.ptr, f32 ? 1 : 0, R, K, tptr(q), tptr(s), tptr(atoms), current_stream()), "mx_quant");
+    return py::make_tuple(q, s, atoms);
+}
+
+py::object gemm_mxfp8(py::object Aq, py::object Asf, py::object Bq, py::object Bsf, bool out_f32) {
+    TensorArg a = tensor_arg(Aq, "torch.uint8"), sa = tensor_arg(Asf, "torch.uint8");
+    TensorArg b = tensor_arg(Bq, "torch.uint8"), sb = tensor_arg(Bsf, "torch.uint8");
+    if (a.shape.size() != 2 || b.shape.size() != 2 || a.shape[1] != b.shape[1])
+        throw std::runtime_error("expected Aq [M,K] and Bq [N,K] e4m3 bytes");
+    const int M = static_cast<int>(a.shape[0]), K = static_cast<int>(a.shape[1]), N = static_cast<int>(b.shape[0]);
+    if (K % 128 != 0) throw std::runtime_error("K must be a multiple of 128");
+    if (static_cast<size_t>(sa.numel()) < dk_mx_sf_bytes(M, K) || static_cast<size_t>(sb.numel()) < dk_mx_sf_bytes(N, K))
+        throw std::runtime_error("scale atom arrays are too small for these operands");
+    py::object c = torch_empty({M, N}, out_f32 ? "float32" : "bfloat16", Aq);
+    throw_on(dk_gemm_mxfp8(a.ptr, sa.ptr, b.ptr, sb.ptr, tptr(c), M, N, K, out_f32 ? 1 : 0, current_stream()),
+             "gemm_mxfp8");
+    return c;
+}
+
+py::tuple moe_quant_pow2(py::object X, py::object row_map, int map_mode, int k) {
+    TensorArg x = tensor_arg(X, "torch.bfloat16");
+    if (x.shape.size() != 2) throw std::runtime_error("X must be [rows, C]");
+    const int C = static_cast<int>(x.shape[1]);
+    int R = static_cast<int>(x.shape[0]);
+    const int* map = nullptr;
+    if (!row_map.is_none()) {
+        TensorArg m = tensor_arg(row_map, "torch.int32");
+        map = static_cast<const int*>(m.ptr);
+        R = static_cast<int>(m.numel());
+        if (map_mode == 0) map_mode = 1;
+    }
+    py::object q = torch_empty({R, C}, "uint8", X);
+    py::object e8 = torch_empty({R / 128, C / 128}, "uint8", X);
+    py::object atoms = torch_empty({R / 128, C / 128, 512}, "uint8", X);
+    throw_on(dk_quant_block128_pow2(x.ptr, R, C, map, map_mode, k, tptr(q), nullptr, tptr(e8), tptr(atoms),
+                                    current_stream()), "moe_quant_pow2");
+    return py::make_tuple(q, e8, atoms);
+}
+
+py::object moe_ffn_mxfp8(py::object Xq, py::object Xa, py::object W13q, py::object W13a, py::object W2q,
+                         py::object W2a, py::object offsets) {
+    TensorArg xq = tensor_arg(Xq, "torch.uint8"), xa = tensor_arg(Xa, "torch.uint8");
+    TensorArg w13q = tensor_arg(W13q, "torch.uint8"), w13a = tensor_arg(W13a, "torch.uint8");
+    TensorArg w2q = tensor_arg(W2q, "torch.uint8"), w2a = tensor_arg(W2a, "torch.uint8");
+    TensorArg off = tensor_arg(offsets, "torch.int32");
+    if (xq.shape.size() != 2 || w13q.shape.size() != 3 || w2q.shape.size() != 3)
+        throw std::runtime_error("expected Xq [R,H], W13q [E,2F,H], W2q [E,H,F]");
+    const int R = static_cast<int>(xq.shape[0]), H = static_cast<int>(xq.shape[1]);
+    const int E = static_cast<int>(w13q.shape[0]), F = static_cast<int>(w13q.shape[1] / 2);
+    if (w13q.shape[2] != H || w2q.shape[0] != E || w2q.shape[1] != H || w2q.shape[2] != F || off.numel() != E + 1)
+        throw std::runtime_error("MoE weight / offset shapes disagree");
+    if (xa.numel() != static_cast<int64_t>(R / 128) * (H / 128) * 512 ||
+        w13a.numel() != static_cast<int64_t>(E) * (2 * F / 128) * (H / 128) * 512 ||
+        w2a.numel() != static_cast<int64_t>(E) * (H / 128) * (F / 128) * 512)
+        throw std::runtime_error("scale atom arrays do not match the operands");
+    py::object hq = torch_empty({R, F}, "uint8", Xq);
+    py::object he = torch_empty({R / 128, F / 128}, "uint8", Xq);
+    py::object ha = torch_empty({R / 128, F / 128, 512}, "uint8", Xq);
+    py::object y = torch_empty({R, H}, "bfloat16", Xq);
+    void* st = current_stream();
+    throw_on(dk_moe_grouped_gemm_mxfp8(xq.ptr, xa.ptr, w13q.ptr, w13a.ptr, static_cast<const int*>(off.ptr), E, R, F,
+                                       H, 1, tptr(hq), tptr(he), tptr(ha), st), "moe_ffn_mxfp8 (gate/up)");
+    throw_on(dk_moe_grouped_gemm_mxfp8(tptr(hq), tptr(ha), w2q.ptr, w2a.ptr, static_cast<const int*>(off.ptr), E, R,
+                                       H, F, 0, tptr(y), nullptr, nullptr, st), "moe_ffn_mxfp8 (down)");
+    return y;
+}
+
 void moe_dispatch(py::object X, py::object topk_idx, py::object row_of_pair, int experts_per_rank,
                   py::object Xrecv, py::object view) {
     TensorArg x = tensor_arg(X, "torch.bfloat16"), ti = tensor_arg(topk_idx, "torch.int32");
@@ -298,6 +376,14 @@ PYBIND11_MODULE(tk_kernel, m) {
           py::arg("k") = 1, "(Xq e4m3 bytes, Xs fp32) with 128x128 block scales; optional row gather");
     m.def("moe_ffn_fp8", &moe_ffn_fp8,
           "Y[R,H] bf16 from Xq, Xs, W13q[E,2F,H], W13s, W2q[E,H,F], W2s, expert_offsets");
+    m.def("mx_quant", &mx_quant, "(q e4m3 bytes [R,K], s e8m0 [R,K/32], scale atoms) from bf16 or fp32 X, 1x32 blocks");
+    m.def("gemm_mxfp8", &gemm_mxfp8, py::arg("Aq"), py::arg("Asf"), py::arg("Bq"), py::arg("Bsf"),
+          py::arg("out_f32") = false, "C[M,N] = dequant(A) @ dequant(B)^T, e4m3 with 1x32 e8m0 scale atoms");
+    m.def("moe_quant_pow2", &moe_quant_pow2, py::arg("X"), py::arg("row_map") = py::none(), py::arg("map_mode") = 0,
+          py::arg("k") = 1, "(Xq e4m3 bytes, e8m0 per 128x128 block, scale atoms) with power-of-two block scales");
+    m.def("moe_ffn_mxfp8", &moe_ffn_mxfp8,
+          "Y[R,H] bf16 from Xq, X atoms, W13q[E,2F,H], W13 atoms, W2q[E,H,F], W2 atoms, expert_offsets "
+          "(power-of-two block scales applied by the tensor core)");
     m.def("moe_dispatch", &moe_dispatch, "push local tokens into the destination ranks' receive rows");
     m.def("moe_combine", &moe_combine, "Out[T_loc,H] = sum_j w_j * Y_dest[row_j]; pulls from peers when world > 1");
     m.def("device_status", &device_status,

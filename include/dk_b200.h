@@ -26,7 +26,8 @@ enum {
     DK_OK = 0,
     DK_ERR_ARG = 1,        /* bad shape, alignment, null pointer, unsupported size */
     DK_ERR_CUDA = 2,       /* a CUDA runtime/driver call failed; see dk_last_error_string() */
-    DK_ERR_DEVICE = 3,     /* a bounded device-side wait gave up; see dk_last_device_status() */
+    DK_ERR_DEVICE = 3,     /* the device holds an unread error record (a bounded wait gave up, or a kernel
+                              skipped a bad index); see dk_last_device_status() */
     DK_ERR_BOOTSTRAP = 4,  /* rendezvous between ranks failed (socket, timeout, peer gone) */
     DK_ERR_NOMEM = 5,      /* symmetric heap exhausted */
     DK_ERR_UNSUPPORTED = 6 /* feature not available on this device/driver */
@@ -55,8 +56,16 @@ const char* dk_last_error_string(void);
 int dk_version(void);
 
 /*
- * Record of the first bounded device-side wait that gave up on the current device since the
- * last call: out = {code, block, site, detail}; code 0 means none. Clears the record.
+ * Record of the first device-side error on the current device since the last call:
+ * out = {code, block, site, detail}; code 0 = none, 1 = a wait inside a CTA gave up, 2 = a wait on
+ * another rank's signal gave up, 3 = a kernel met an index from device memory (expert id, row,
+ * offset) that points outside its buffers and skipped the access. Clears the record.
+ *
+ * Launches are asynchronous: DK_OK from an entry point means "launched", not "completed". While a
+ * record is unread, every collective entry point (dk_allreduce, dk_gemm_rs, dk_gemm_rs_phase,
+ * dk_peer_barrier*, dk_allgather, dk_moe_dispatch, dk_moe_combine_ep, dk_moe_ep_layer) returns
+ * DK_ERR_DEVICE without launching and leaves the record in place: after a wait has run out the
+ * ranks are out of step, and later waits on peers would give up at once and leave wrong results.
  * The reference has no counterpart (HIP errors are printed and dropped, include/pyutils/util.cuh:10-16).
  */
 int dk_last_device_status(unsigned out[4]);
@@ -274,6 +283,55 @@ int dk_moe_combine(const void* y, const int* row_of_pair, const float* topk_w, i
 int dk_moe_grouped_gemm_fp8(const void* xq, const float* xs, const void* wq, const float* ws,
                             const int* offsets, int E, int R, int N, int K, int gated, void* out,
                             float* out_scales, void* stream);
+
+/* ------------------------------------------------------------------ MXFP8 (1x32 e8m0 block scales) */
+/*
+ * The block-scaled fp8 format the reference ships: e4m3 elements with one e8m0 (power-of-two) scale
+ * per 32 consecutive elements of K. Here the tensor core applies the scales itself
+ * (tcgen05.mma.kind::mxf8f6f4.block_scale reads them from tensor memory).
+ *
+ * Scale "atoms": the layout the tensor core wants. For every 128 rows x 128 elements of K one
+ * 512-byte atom, byte r0*16 + r1*4 + g = scale of row r0 + 32*r1 (inside the 128-row block) for
+ * the 32-element group g; atoms are ordered [row block][K block]. dk_mx_sf_bytes(R, K) is the size
+ * of the atom array for an [R, K] operand (R rounded up to 128 rows).
+ *
+ * dk_mx_quant: x [R, K] (bf16, or fp32 when x_is_f32) -> q e4m3 bytes [R, K], the scales row-major
+ * s_rows [R, K/32] (may be NULL) and as atoms. scale = clamp(floor(log2(amax)) + 127, 0, 254), 0 for
+ * an all-zero block; q = e4m3(x * 2^(127 - scale)), round to nearest even. K % 128 == 0.
+ * Replaces the reference's host quantiser, compute_e8m0 and its loop
+ * (kernels/cdna4/gemm/mxfp8/MXFP8_8wave/8_wave_NT.cu:286-327,
+ * tests/unit/cdna4/warp/register/tile/mma_scaled.cu:200-232); the atoms replace its per-iteration
+ * packed scale words (mma_scaled.cu:249-264).
+ *
+ * dk_gemm_mxfp8: C[M, N] = dequant(A) dequant(B)^T with A [M, K], B [N, K] e4m3 bytes and their
+ * scale atoms; fp32 accumulation in tensor memory; C bf16 (out_f32 = 0) or fp32 (out_f32 = 1).
+ * K % 128 == 0, N % 8 == 0. Replaces the reference's MXFP8 GEMM kernel (8_wave_NT.cu:432-496,
+ * scaled MFMA at :39-44) and the register-tile op its fixture tests (mma_scaled.cu:107-198).
+ */
+size_t dk_mx_sf_bytes(int R, int K);
+int dk_mx_quant(const void* x, int x_is_f32, int R, int K, void* q, void* s_rows, void* sf_atoms,
+                void* stream);
+int dk_gemm_mxfp8(const void* aq, const void* sfa, const void* bq, const void* sfb, void* C, int M, int N,
+                  int K, int out_f32, void* stream);
+/*
+ * The MoE path on the same instruction, for 128x128 block scales that are powers of two (a
+ * second quantisation mode beside the fp32 scales of dk_quant_block128 / dk_moe_grouped_gemm_fp8;
+ * no reference counterpart, as for the other MoE entry points).
+ *
+ * dk_quant_block128_pow2: as dk_quant_block128 with s = 2^ceil(log2(amax/448)) (1 for an all-zero
+ * block); besides q it writes s (fp32, may be NULL), e8 = log2(s) + 127 as bytes [R/128, C/128] (may
+ * be NULL) and the scale atoms [R/128][C/128][512] (the block's byte for all of its rows and groups).
+ *
+ * dk_moe_grouped_gemm_mxfp8: as dk_moe_grouped_gemm_fp8 with scale atoms in place of the fp32
+ * scales: x_atoms [R/128][K/128][512], w_atoms [E * rows/128][K/128][512]. gated = 1 writes e4m3
+ * bytes [R, N] of silu(gate) * up requantised per 128x128 block with a power-of-two scale, out_e8
+ * [R/128, N/128] and out_atoms [R/128][N/128][512]; gated = 0 writes bf16 [R, N].
+ */
+int dk_quant_block128_pow2(const void* x, int R, int C, const int* row_map, int map_mode, int k, void* q,
+                           float* s, void* e8, void* sf_atoms, void* stream);
+int dk_moe_grouped_gemm_mxfp8(const void* xq, const void* x_atoms, const void* wq, const void* w_atoms,
+                              const int* offsets, int E, int R, int N, int K, int gated, void* out,
+                              void* out_e8, void* out_atoms, void* stream);
 
 /* ------------------------------------------------------------------ expert-parallel exchange */
 /*

@@ -263,6 +263,17 @@ def moe_ffn_ref(xq, xs, w13q, w13s, w2q, w2s, offsets):
     return y, hq, hs
 
 
+def moe_ffn_pow2_ref(xq, xs, w13q, w13s, w2q, w2s, offsets):
+    """moe_ffn_ref with the intermediate requantised by quant_block128_pow2 (the scales handed in
+    are powers of two as well; the arithmetic is the same block dequantisation).
+    Returns (Y fp32 [R,H], hq u8 [R,F], hs fp32, h_e8 u8)."""
+    gu = grouped_gemm_ref(xq, xs, w13q, w13s, offsets)
+    h = silu_mul(gu)
+    hq, hs, he = quant_block128_pow2(h)
+    y = grouped_gemm_ref(hq, hs, w2q, w2s, offsets)
+    return y, hq, hs, he
+
+
 def moe_combine_ref(y: torch.Tensor, row_of_pair: torch.Tensor, topk_w: torch.Tensor):
     """out[t] = sum_j w[t,j] * Y[row(t,j)] in fp32 (slot order)."""
     T, k = row_of_pair.shape
