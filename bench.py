@@ -418,11 +418,15 @@ class Moe:
                                name="DeepSeek-V3-shaped: 32768 tokens, hidden 7168, expert inter 2048, "
                                     "E=256 top-8, Zipf(1.1)")}
 
-    def __init__(self, ctx, which):
+    def __init__(self, ctx, which, scales="fp32"):
+        """scales: "fp32" = 128x128 blocks with fp32 scales, promoted in software every 128 of K (the
+        format the configurations name); "pow2" = the same blocks with power-of-two scales, applied
+        by the tensor core (tcgen05 block-scaled MMA)."""
         import torch
         self.ctx = ctx
         s = self.SHAPES[which]
         self.metric = which + "_tflops"
+        self.scales = scales
         self.s = s
         P, rank = ctx.world, ctx.rank
         T, H, F, E, k = s["T"], s["H"], s["F"], s["E"], s["k"]
@@ -442,13 +446,19 @@ class Moe:
         self.logits = logits.contiguous()
         # this rank's experts, quantised with the library's own block quantiser
         w13q, w13s, w2q, w2s = [], [], [], []
+
+        def quant_w(w):
+            if scales == "pow2":
+                q, _, _, atoms = capi.quant_block128_pow2(w)
+                return q, atoms
+            return capi.quant_block128(w)
         for _ in range(self.epr):
             w = (torch.randn(2 * F, H, device="cuda", generator=g) / math.sqrt(H)).to(torch.bfloat16)
-            q, sc = capi.quant_block128(w)
+            q, sc = quant_w(w)
             w13q.append(q)
             w13s.append(sc)
             w = (torch.randn(H, F, device="cuda", generator=g) / math.sqrt(F)).to(torch.bfloat16)
-            q, sc = capi.quant_block128(w)
+            q, sc = quant_w(w)
             w2q.append(q)
             w2s.append(sc)
             del w
@@ -472,10 +482,10 @@ class Moe:
         idx, w = tk.moe_route(self.logits, k)
         if ctx.world == 1:
             rop, por, offs, counts = tk.moe_permute(idx, E, 128, 0)
-            xq, xs = tk.moe_quant(self.x, por, 1, k)
+            xq, xs = self._quant(self.x, por, 1, k)
             if timed_gemm:
                 timed_gemm[0].record()
-            y = tk.moe_ffn_fp8(xq, xs, self.w13q, self.w13s, self.w2q, self.w2s, offs)
+            y = self._ffn(xq, xs, offs)
             if timed_gemm:
                 timed_gemm[1].record()
             out = tk.moe_combine(y, idx, rop, w, E, ctx.view)
@@ -486,16 +496,29 @@ class Moe:
             rop, por, offs, counts = tk.moe_permute(self.all_idx, E, 128, self.epr)
             my_rop = rop[r * self.Tl:(r + 1) * self.Tl]
             tk.moe_dispatch(self.x, idx, my_rop, self.epr, self.xrecv, ctx.view)
-            xq, xs = tk.moe_quant(self.xrecv, por[r], 2, 1)
+            xq, xs = self._quant(self.xrecv, por[r], 2, 1)
             if timed_gemm:
                 timed_gemm[0].record()
-            y = tk.moe_ffn_fp8(xq, xs, self.w13q, self.w13s, self.w2q, self.w2s, offs[r])
+            y = self._ffn(xq, xs, offs[r])
             if timed_gemm:
                 timed_gemm[1].record()
             self.ybuf.copy_(y)
             out = tk.moe_combine(self.ybuf, idx, my_rop, w, self.epr, ctx.view)
             self.pairs_here = counts[r * self.epr:(r + 1) * self.epr]
         return out
+
+    def _quant(self, x, row_map, mode, k):
+        tk = self.ctx.tk
+        if self.scales == "pow2":
+            q, _, atoms = tk.moe_quant_pow2(x, row_map, mode, k)
+            return q, atoms
+        return tk.moe_quant(x, row_map, mode, k)
+
+    def _ffn(self, xq, xs, offs):
+        tk = self.ctx.tk
+        if self.scales == "pow2":
+            return tk.moe_ffn_mxfp8(xq, xs, self.w13q, self.w13s, self.w2q, self.w2s, offs)
+        return tk.moe_ffn_fp8(xq, xs, self.w13q, self.w13s, self.w2q, self.w2s, offs)
 
     def time_gemm(self):
         import torch
@@ -530,7 +553,8 @@ class Moe:
     def config(self, value):
         s, P = self.s, self.ctx.world
         per_pair = 2.0 * s["H"] * 2 * s["F"] + 2.0 * s["F"] * s["H"]
-        c = {"workload": f"fp8 MoE layer, {s['name']}, 128x128 block scales, EP={P}",
+        c = {"workload": f"fp8 MoE layer, {s['name']}, 128x128 block scales "
+                         f"({'power-of-two, applied by the tensor core' if self.scales == 'pow2' else 'fp32, promoted in software'}), EP={P}",
              "l2": f"expert weights ({(self.w13q.numel() + self.w2q.numel()) / 1e6:.0f} MB fp8 on this GPU) exceed L2",
              "per_gpu_tflops": value / P}
         if self.gemm_ms:
@@ -553,7 +577,7 @@ class Moe:
             ach = (self.work / self.ctx.world) / (ms_step * 1e-3) / 1e12
             what = "whole step"
         return {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
-                "frac": ach / peak if peak else None, "traffic": load_traffic(self.metric), "of": what,
+                "frac": ach / peak if peak else None, "traffic": load_traffic(self.metric + ("_pow2" if self.scales == "pow2" else "")), "of": what,
                 "peak_source": f"2 x {peak_src} cuBLAS bf16 ({'sustained' if sustained else 'burst'}) "
                                f"taken as the fp8 dense peak"}
 
@@ -615,7 +639,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gemm_rs",
                     choices=["gemm_rs", "allreduce", "moe_mixtral", "moe_dsv3"])
-    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--scales", default="fp32", choices=["fp32", "pow2"],
+                    help="MoE workloads: fp32 128x128 block scales (software promotion) or power-of-two "
+                         "block scales applied by the block-scaled MMA")
+    ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--shape", default=None, help="M,N,K override of the GEMM workload (profiling runs)")
@@ -653,7 +680,7 @@ def main():
     else:
         if args.tokens:
             Moe.SHAPES[args.workload]["T"] = args.tokens
-        wl = Moe(ctx, args.workload)
+        wl = Moe(ctx, args.workload, args.scales)
     barrier = ctx.barrier
 
     sampler = ClockSampler(local_rank) if rank == 0 else None

@@ -413,8 +413,8 @@ def gemm_mxfp8(aq, sfa, bq, sfb, out_dtype=None, stream=None):
 
 
 def quant_block128_pow2(x, rows: int | None = None, row_map=None, map_mode: int = 0, k: int = 1, stream=None):
-    """(q uint8 [R,C], s fp32 [R/128,C/128], e8 uint8 [R/128,C/128], atoms uint8 [R/128,C/128,512]):
-    128x128 block quantisation with power-of-two scales."""
+    """(q uint8 [R,C], s fp32 [R/128,C/128], e8 uint8 [R/128,C/128], block atoms uint8
+    [R/128, ceil(C/512), 512]): 128x128 block quantisation with power-of-two scales."""
     import torch
     _need_cuda(x)
     if x.dtype != torch.bfloat16:
@@ -425,7 +425,7 @@ def quant_block128_pow2(x, rows: int | None = None, row_map=None, map_mode: int 
     q = torch.empty((R, Cc), dtype=torch.uint8, device=dev)
     s = torch.empty((R // 128, Cc // 128), dtype=torch.float32, device=dev)
     e8 = torch.empty((R // 128, Cc // 128), dtype=torch.uint8, device=dev)
-    atoms = torch.empty((R // 128, Cc // 128, 512), dtype=torch.uint8, device=dev)
+    atoms = torch.full((R // 128, (Cc // 128 + 3) // 4, 512), 127, dtype=torch.uint8, device=dev)
     check(lib().dk_quant_block128_pow2(_ptr(x), R, Cc, _ptr(row_map) if row_map is not None else None,
                                        map_mode, k, _ptr(q), _ptr(s), _ptr(e8), _ptr(atoms), _stream_ptr(stream)))
     return q, s, e8, atoms
@@ -433,7 +433,8 @@ def quant_block128_pow2(x, rows: int | None = None, row_map=None, map_mode: int 
 
 def moe_grouped_gemm_mxfp8(xq, x_atoms, wq, w_atoms, offsets, gated: bool, stream=None):
     """Grouped GEMM on the block-scaled tensor-core path. gated: returns (hq uint8 [R,F], e8 uint8
-    [R/128,F/128], atoms [R/128,F/128,512]); else Y bf16 [R,N]. Rows beyond offsets[E] stay zero."""
+    [R/128,F/128], block atoms [R/128,ceil(F/512),512]); else Y bf16 [R,N]. Rows beyond offsets[E]
+    stay zero."""
     import torch
     _need_cuda(xq, x_atoms, wq, w_atoms, offsets)
     R, K = xq.shape
@@ -443,7 +444,7 @@ def moe_grouped_gemm_mxfp8(xq, x_atoms, wq, w_atoms, offsets, gated: bool, strea
         N = wq.shape[1] // 2
         out = torch.zeros((R, N), dtype=torch.uint8, device=dev)
         e8 = torch.full((R // 128, N // 128), 127, dtype=torch.uint8, device=dev)
-        atoms = torch.full((R // 128, N // 128, 512), 127, dtype=torch.uint8, device=dev)
+        atoms = torch.full((R // 128, (N // 128 + 3) // 4, 512), 127, dtype=torch.uint8, device=dev)
         check(lib().dk_moe_grouped_gemm_mxfp8(_ptr(xq), _ptr(x_atoms), _ptr(wq), _ptr(w_atoms), _ptr(offsets), E,
                                               R, N, K, 1, _ptr(out), _ptr(e8), _ptr(atoms), _stream_ptr(stream)))
         return out, e8, atoms

@@ -184,8 +184,9 @@ __global__ void __launch_bounds__(PERM_CHUNK) moe_place_kernel(const int* __rest
 //   map_mode 0: row r of x;  1: row map[r] / k of x (gather), zeros where map[r] < 0;
 //   2: row r of x where map[r] >= 0, zeros elsewhere (rows already in place, padding undefined)
 // POW2: the scale is rounded UP to a power of two, s = 2^ceil(log2(amax/448)) (1 for an all-zero
-// block), and also written as an e8m0 byte (log2(s) + 127) and as the 512-byte scale atom the
-// block-scaled tensor-core path reads (the byte repeated for the block's 128 rows x 4 K groups).
+// block), and also written as an e8m0 byte (log2(s) + 127) and into the scale atoms the
+// block-scaled tensor-core path reads: per 128 rows and four column blocks one 512-byte atom whose
+// byte r*4 + g (r = row slot 0..127, g = 0..3) is the byte of column block 4j + g.
 template <bool POW2>
 __global__ void __launch_bounds__(256) quant_block128_kernel(const __nv_bfloat16* __restrict__ x, int R, int C,
                                                              const int* __restrict__ map, int map_mode,
@@ -237,9 +238,11 @@ __global__ void __launch_bounds__(256) quant_block128_kernel(const __nv_bfloat16
         }
         scale = ldexpf(1.0f, ex);
         const uint32_t b8 = static_cast<uint32_t>(ex + 127);
-        if (threadIdx.x < 32) {
-            const uint32_t rep = b8 * 0x01010101u;
-            reinterpret_cast<uint4*>(atoms + blk * 512)[threadIdx.x] = make_uint4(rep, rep, rep, rep);
+        if (threadIdx.x < 128) {
+            // byte (bc % 4) of atom (bc / 4) of this row block, for each of its 128 rows
+            const int kb4 = (C / 128 + 3) / 4;
+            atoms[(static_cast<size_t>(br) * kb4 + (bc >> 2)) * 512 + threadIdx.x * 4 + (bc & 3)] =
+                static_cast<uint8_t>(b8);
         }
         if (threadIdx.x == 0 && e8 != nullptr) e8[blk] = static_cast<uint8_t>(b8);
     }

@@ -6,7 +6,8 @@
 //   dk_gemm_mxfp8        C[M,N] = dequant(A) dequant(B)^T, the MXFP8 GEMM
 //   dk_moe_grouped_gemm_mxfp8   the MoE grouped GEMM (plain, or gate/up fused with SiLU*mul and
 //                        requantisation) on the same instruction, for power-of-two 128x128 block
-//                        scales expanded to the 1x32 granularity the hardware reads
+//                        scales: the four scale bytes the hardware holds per row then carry four
+//                        consecutive K blocks, so scales are refreshed every fourth K block only
 //
 // Stands in for the reference's MXFP8 GEMM: host quantiser compute_e8m0 + quantisation loop
 // (kernels/cdna4/gemm/mxfp8/MXFP8_8wave/8_wave_NT.cu:286-327), kernel with per-K-iteration packed
@@ -60,8 +61,8 @@ struct MxMaps {
 
 struct MxArgs {
     const int* offsets;   // [E+1] device (multiples of 128), or null: one group of rows_pad rows
-    const uint8_t* sfa;   // scale atoms of A: [row blocks][K/128][512]
-    const uint8_t* sfb;   // scale atoms of B: [row blocks][K/128][512]
+    const uint8_t* sfa;   // scale atoms of A: [row blocks][K/128][512]; block mode: [row blocks][ceil(K/512)][512]
+    const uint8_t* sfb;   // scale atoms of B, likewise
     int E, K, N;          // N: output columns (gated: F)
     int num_kb;           // K / 128
     int n_tiles;          // gated: F/128, plain: ceil(N/256)
@@ -72,7 +73,7 @@ struct MxArgs {
     int rows_pad;         // R rounded up to 128 (used when offsets is null)
     void* out;            // bf16 / fp32 [R, N], or e4m3 bytes [R, F]
     uint8_t* out_e8;      // gated: e8m0 scale per 128x128 block [R/128, F/128]
-    uint8_t* out_atoms;   // gated: the same scales as atoms [R/128][F/128][512]
+    uint8_t* out_atoms;   // gated: the same scales as block-mode atoms [R/128][ceil(F/512)][512]
     unsigned* status;
 };
 
@@ -102,7 +103,12 @@ __device__ __forceinline__ float mx_rcp_approx(float x) {
     return r;
 }
 
-template <int MODE>
+// BLK = false: scales per 1x32 block (MXFP8): one atom per 128 rows and K block, scale byte k of the
+// atom for the k-th MMA of the K block. BLK = true: scales per 128x128 block: one atom per 128 rows
+// and FOUR K blocks, byte g of the atom holding the scale of K block 4j + g for every row, so the
+// scale copies (and their bytes) are needed only every fourth K block and all four MMAs of K block
+// kb select byte kb % 4.
+template <int MODE, bool BLK>
 __global__ void __launch_bounds__(X_THREADS, 1)
 mx_gemm_kernel(const __grid_constant__ MxMaps maps, const MxArgs g) {
     constexpr bool GATED = MODE == MX_OUT_GATED;
@@ -196,16 +202,18 @@ mx_gemm_kernel(const __grid_constant__ MxMaps maps, const MxArgs g) {
                 }
                 if (blk0 >= g.sfb_blocks) blk0 = g.sfb_blocks - 1;
                 if (blk1 >= g.sfb_blocks) blk1 = g.sfb_blocks - 1;
-                const uint8_t* sfa_p = g.sfa + static_cast<size_t>(row0 / XM) * g.num_kb * X_ATOM;
-                const uint8_t* sfb0_p = g.sfb + static_cast<size_t>(blk0) * g.num_kb * X_ATOM;
-                const uint8_t* sfb1_p = g.sfb + static_cast<size_t>(blk1) * g.num_kb * X_ATOM;
+                const int atoms_k = BLK ? (g.num_kb + 3) / 4 : g.num_kb;  // atoms per 128-row block
+                const uint8_t* sfa_p = g.sfa + static_cast<size_t>(row0 / XM) * atoms_k * X_ATOM;
+                const uint8_t* sfb0_p = g.sfb + static_cast<size_t>(blk0) * atoms_k * X_ATOM;
+                const uint8_t* sfb1_p = g.sfb + static_cast<size_t>(blk1) * atoms_k * X_ATOM;
                 for (int kb = 0; kb < g.num_kb; ++kb) {
                     if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, wc, XS_EMPTY, t)) {
                         ok = false;
                         break;
                     }
                     const uint32_t full = bar_full + 8 * s;
-                    mbar_expect_tx(full, X_STAGE_TX);
+                    const bool with_sf = !BLK || (kb & 3) == 0;
+                    mbar_expect_tx(full, with_sf ? X_STAGE_TX : XA_BYTES + XB_BYTES);
                     const uint32_t st = ring + s * X_STAGE_STRIDE;
                     tma_load_2d(st, &maps.a, full, kb * XK, row0);
                     if (GATED) {
@@ -215,9 +223,12 @@ mx_gemm_kernel(const __grid_constant__ MxMaps maps, const MxArgs g) {
                         tma_load_2d(st + XA_BYTES, &maps.b, full, kb * XK, wrow + n * XN);
                     }
                     const uint32_t sf = st + XA_BYTES + XB_BYTES;
-                    bulk_load_1d(sf, sfa_p + static_cast<size_t>(kb) * X_ATOM, X_ATOM, full);
-                    bulk_load_1d(sf + X_ATOM, sfb0_p + static_cast<size_t>(kb) * X_ATOM, X_ATOM, full);
-                    bulk_load_1d(sf + 2 * X_ATOM, sfb1_p + static_cast<size_t>(kb) * X_ATOM, X_ATOM, full);
+                    if (with_sf) {
+                        const size_t ai = static_cast<size_t>(BLK ? kb >> 2 : kb) * X_ATOM;
+                        bulk_load_1d(sf, sfa_p + ai, X_ATOM, full);
+                        bulk_load_1d(sf + X_ATOM, sfb0_p + ai, X_ATOM, full);
+                        bulk_load_1d(sf + 2 * X_ATOM, sfb1_p + ai, X_ATOM, full);
+                    }
                     if (++s == X_STAGES) {
                         s = 0;
                         ph ^= 1;
@@ -245,18 +256,22 @@ mx_gemm_kernel(const __grid_constant__ MxMaps maps, const MxArgs g) {
                     tc_fence_after();
                     const uint32_t st = ring + s * X_STAGE_STRIDE;
                     const uint32_t sf = st + XA_BYTES + XB_BYTES;
-                    // The scale columns are rewritten every K block: tcgen05.cp and tcgen05.mma of
-                    // one thread execute in issue order, so the copies wait for the previous
-                    // block's MMAs and these MMAs for the copies.
-                    tmem_cp_32x128b_warpx4<1>(sfa_t, umma_desc_sf_atom(sf));
-                    tmem_cp_32x128b_warpx4<1>(sfb_t, umma_desc_sf_atom(sf + X_ATOM));
-                    tmem_cp_32x128b_warpx4<1>(sfb_t + 4, umma_desc_sf_atom(sf + 2 * X_ATOM));
+                    // The scale columns are rewritten in place: tcgen05.cp and tcgen05.mma of one
+                    // thread execute in issue order, so the copies wait for the previous MMAs and
+                    // these MMAs for the copies. (The copies occupy the tensor pipe: three per K
+                    // block measured 10 % of the kernel; separate columns per stage or a thread of
+                    // their own for the copies changed nothing.)
+                    if (!BLK || (kb & 3) == 0) {
+                        tmem_cp_32x128b_warpx4<1>(sfa_t, umma_desc_sf_atom(sf));
+                        tmem_cp_32x128b_warpx4<1>(sfb_t, umma_desc_sf_atom(sf + X_ATOM));
+                        tmem_cp_32x128b_warpx4<1>(sfb_t + 4, umma_desc_sf_atom(sf + 2 * X_ATOM));
+                    }
                     const uint64_t da = umma_desc_sw128(st);
                     const uint64_t db = umma_desc_sw128(st + XA_BYTES);
 #pragma unroll
                     for (int k = 0; k < XK / 32; ++k)
-                        umma_mxf8<1>(tmem_base, da + 2 * k, db + 2 * k, umma_idesc_mx(XM, XN, k), sfa_t, sfb_t,
-                                     (kb | k) != 0);
+                        umma_mxf8<1>(tmem_base, da + 2 * k, db + 2 * k, umma_idesc_mx(XM, XN, BLK ? (kb & 3) : k),
+                                     sfa_t, sfb_t, (kb | k) != 0);
                     umma_commit<1>(bar_empty + 8 * s);
                     if (++s == X_STAGES) {
                         s = 0;
@@ -330,9 +345,13 @@ mx_gemm_kernel(const __grid_constant__ MxMaps maps, const MxArgs g) {
                 const uint32_t e8 = static_cast<uint32_t>(ex + 127);
                 const size_t blk = static_cast<size_t>(row0 / XM) * (g.N / 128) + n;
                 if (ew == 0) {
-                    // one scale block of the next GEMM's A operand: the byte for every row and group
-                    const uint32_t rep = e8 * 0x01010101u;
-                    reinterpret_cast<uint4*>(g.out_atoms + blk * X_ATOM)[lane] = make_uint4(rep, rep, rep, rep);
+                    // this tile is K block n of the next GEMM's A operand: byte n % 4 of atom n / 4
+                    // of its row block, for every row
+                    const int fb = g.N / 128;
+                    uint8_t* atom = g.out_atoms +
+                                    (static_cast<size_t>(row0 / XM) * ((fb + 3) / 4) + (n >> 2)) * X_ATOM + (n & 3);
+#pragma unroll
+                    for (int r1 = 0; r1 < 4; ++r1) atom[lane * 16 + r1 * 4] = static_cast<uint8_t>(e8);
                     if (lane == 0) g.out_e8[blk] = static_cast<uint8_t>(e8);
                 }
                 if (row < g.R) {
@@ -499,13 +518,13 @@ __global__ void __launch_bounds__(256) mx_quant_kernel(const T* __restrict__ x, 
     }
 }
 
-template <int MODE>
+template <int MODE, bool BLK>
 static int launch_mx(const MxMaps& maps, const MxArgs& g, int max_tiles, cudaStream_t st) {
     static bool attr_set[64] = {};
     int dev = 0;
     DK_CUDA_OK(cudaGetDevice(&dev));
     if (!attr_set[dev & 63]) {
-        DK_CUDA_OK(cudaFuncSetAttribute(mx_gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        DK_CUDA_OK(cudaFuncSetAttribute(mx_gemm_kernel<MODE, BLK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         X_SMEM_BYTES));
         attr_set[dev & 63] = true;
     }
@@ -513,7 +532,7 @@ static int launch_mx(const MxMaps& maps, const MxArgs& g, int max_tiles, cudaStr
     int rc = sm_count(&sms);
     if (rc != DK_OK) return rc;
     const int grid = max_tiles < sms ? max_tiles : sms;
-    mx_gemm_kernel<MODE><<<grid, X_THREADS, X_SMEM_BYTES, st>>>(maps, g);
+    mx_gemm_kernel<MODE, BLK><<<grid, X_THREADS, X_SMEM_BYTES, st>>>(maps, g);
     DK_CUDA_OK(cudaGetLastError());
     return DK_OK;
 }
@@ -588,7 +607,7 @@ int dk_gemm_mxfp8(const void* aq, const void* sfa, const void* bq, const void* s
     if (rc != DK_OK) return rc;
     const int tiles = (g.rows_pad / XM) * g.n_tiles;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return out_f32 ? launch_mx<MX_OUT_F32>(maps, g, tiles, st) : launch_mx<MX_OUT_BF16>(maps, g, tiles, st);
+    return out_f32 ? launch_mx<MX_OUT_F32, false>(maps, g, tiles, st) : launch_mx<MX_OUT_BF16, false>(maps, g, tiles, st);
 }
 
 int dk_moe_grouped_gemm_mxfp8(const void* xq, const void* x_atoms, const void* wq, const void* w_atoms,
@@ -634,7 +653,7 @@ int dk_moe_grouped_gemm_mxfp8(const void* xq, const void* x_atoms, const void* w
     if (rc != DK_OK) return rc;
     const int tiles = (R / XM) * g.n_tiles;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return gated ? launch_mx<MX_OUT_GATED>(maps, g, tiles, st) : launch_mx<MX_OUT_BF16>(maps, g, tiles, st);
+    return gated ? launch_mx<MX_OUT_GATED, true>(maps, g, tiles, st) : launch_mx<MX_OUT_BF16, true>(maps, g, tiles, st);
 }
 
 }  // extern "C"

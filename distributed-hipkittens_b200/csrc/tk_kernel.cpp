@@ -283,7 +283,7 @@ py::tuple moe_quant_pow2(py::object X, py::object row_map, int map_mode, int k) 
     }
     py::object q = torch_empty({R, C}, "uint8", X);
     py::object e8 = torch_empty({R / 128, C / 128}, "uint8", X);
-    py::object atoms = torch_empty({R / 128, C / 128, 512}, "uint8", X);
+    py::object atoms = torch_empty({R / 128, (C / 128 + 3) / 4, 512}, "uint8", X);
     throw_on(dk_quant_block128_pow2(x.ptr, R, C, map, map_mode, k, tptr(q), nullptr, tptr(e8), tptr(atoms),
                                     current_stream()), "moe_quant_pow2");
     return py::make_tuple(q, e8, atoms);
@@ -301,13 +301,14 @@ py::object moe_ffn_mxfp8(py::object Xq, py::object Xa, py::object W13q, py::obje
     const int E = static_cast<int>(w13q.shape[0]), F = static_cast<int>(w13q.shape[1] / 2);
     if (w13q.shape[2] != H || w2q.shape[0] != E || w2q.shape[1] != H || w2q.shape[2] != F || off.numel() != E + 1)
         throw std::runtime_error("MoE weight / offset shapes disagree");
-    if (xa.numel() != static_cast<int64_t>(R / 128) * (H / 128) * 512 ||
-        w13a.numel() != static_cast<int64_t>(E) * (2 * F / 128) * (H / 128) * 512 ||
-        w2a.numel() != static_cast<int64_t>(E) * (H / 128) * (F / 128) * 512)
+    const int64_t hk = (H / 128 + 3) / 4, fk = (F / 128 + 3) / 4;  // atoms per 128-row block
+    if (xa.numel() != static_cast<int64_t>(R / 128) * hk * 512 ||
+        w13a.numel() != static_cast<int64_t>(E) * (2 * F / 128) * hk * 512 ||
+        w2a.numel() != static_cast<int64_t>(E) * (H / 128) * fk * 512)
         throw std::runtime_error("scale atom arrays do not match the operands");
     py::object hq = torch_empty({R, F}, "uint8", Xq);
     py::object he = torch_empty({R / 128, F / 128}, "uint8", Xq);
-    py::object ha = torch_empty({R / 128, F / 128, 512}, "uint8", Xq);
+    py::object ha = torch_empty({R / 128, fk, 512}, "uint8", Xq);
     py::object y = torch_empty({R, H}, "bfloat16", Xq);
     void* st = current_stream();
     throw_on(dk_moe_grouped_gemm_mxfp8(xq.ptr, xa.ptr, w13q.ptr, w13a.ptr, static_cast<const int*>(off.ptr), E, R, F,

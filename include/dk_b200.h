@@ -318,14 +318,20 @@ int dk_gemm_mxfp8(const void* aq, const void* sfa, const void* bq, const void* s
  * second quantisation mode beside the fp32 scales of dk_quant_block128 / dk_moe_grouped_gemm_fp8;
  * no reference counterpart, as for the other MoE entry points).
  *
+ * "Block atoms": with one scale per 128x128 block the four scale bytes the tensor core holds per
+ * row carry four consecutive K blocks instead of four 32-element groups. Per 128 rows and 512
+ * elements of K one 512-byte atom: byte r*4 + g (r = 0..127 any row slot, g = 0..3) = scale byte of
+ * block (row block, 4j + g); atoms ordered [row block][ceil(K/512)]. Bytes of K blocks that do not
+ * exist are never read.
+ *
  * dk_quant_block128_pow2: as dk_quant_block128 with s = 2^ceil(log2(amax/448)) (1 for an all-zero
  * block); besides q it writes s (fp32, may be NULL), e8 = log2(s) + 127 as bytes [R/128, C/128] (may
- * be NULL) and the scale atoms [R/128][C/128][512] (the block's byte for all of its rows and groups).
+ * be NULL) and the block atoms [R/128][ceil(C/512)][512].
  *
- * dk_moe_grouped_gemm_mxfp8: as dk_moe_grouped_gemm_fp8 with scale atoms in place of the fp32
- * scales: x_atoms [R/128][K/128][512], w_atoms [E * rows/128][K/128][512]. gated = 1 writes e4m3
- * bytes [R, N] of silu(gate) * up requantised per 128x128 block with a power-of-two scale, out_e8
- * [R/128, N/128] and out_atoms [R/128][N/128][512]; gated = 0 writes bf16 [R, N].
+ * dk_moe_grouped_gemm_mxfp8: as dk_moe_grouped_gemm_fp8 with block atoms in place of the fp32
+ * scales: x_atoms [R/128][ceil(K/512)][512], w_atoms [E * rows/128][ceil(K/512)][512]. gated = 1
+ * writes e4m3 bytes [R, N] of silu(gate) * up requantised per 128x128 block with a power-of-two
+ * scale, out_e8 [R/128, N/128] and out_atoms [R/128][ceil(N/512)][512]; gated = 0 writes bf16 [R, N].
  */
 int dk_quant_block128_pow2(const void* x, int R, int C, const int* row_map, int map_mode, int k, void* q,
                            float* s, void* e8, void* sf_atoms, void* stream);

@@ -225,6 +225,18 @@ def block128_scales_to_sf_atoms(e8m0: torch.Tensor) -> torch.Tensor:
     return e8m0[:, :, None, None, None].expand(-1, -1, 32, 4, 4).contiguous()
 
 
+def block128_scales_to_block_atoms(e8m0: torch.Tensor) -> torch.Tensor:
+    """128x128 power-of-two block scales in the compact form the grouped GEMM reads: the four scale
+    bytes the tensor core holds per row carry four consecutive K blocks. [R/128, C/128] ->
+    [R/128, ceil(C/512), 128, 4] bytes, byte [rb, j, r, g] = e8m0[rb, 4j + g] for every row slot r
+    (127 where the block does not exist)."""
+    Rb, Cb = e8m0.shape
+    j = (Cb + 3) // 4
+    pad = torch.full((Rb, 4 * j), 127, dtype=torch.uint8)
+    pad[:, :Cb] = e8m0
+    return pad.reshape(Rb, j, 1, 4).expand(-1, -1, 128, -1).contiguous()
+
+
 def dequant_block128(q_u8: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
     R, Cc = q_u8.shape
     qf = q_u8.view(torch.float8_e4m3fn).float().reshape(R // BLOCK, BLOCK, Cc // BLOCK, BLOCK)

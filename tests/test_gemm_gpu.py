@@ -109,10 +109,17 @@ def test_dispatch_micro_three_argument_form(orc, m, n, k):
     ref = orc.gemm_ref(A, Bt)
     got = C.float().cpu()
     assert orc.rel_fro(got, ref) <= TOL
-    # outputs are ~N(0, K); an element of magnitude below ~1 has cancelled three or more digits and
-    # cannot be held to 1 % by any summation order, so the criterion is asked of 95 % of the elements
-    inside = torch.isclose(got, ref, rtol=1e-2, atol=1e-8).float().mean().item()
-    assert inside >= 0.95, inside
+    # The reference compares with allclose(rtol=1e-2) against a bf16 matmul (test.py:29-31). Outputs
+    # are ~N(0, K); an element that nearly cancels cannot meet a purely relative bound in bf16 under
+    # any summation order, so every element is held to rtol 1e-2 plus an absolute floor scaled to the
+    # output, 1e-2 * sqrt(K), against the bf16-rounded reference.
+    ref16 = ref.to(torch.bfloat16).float()
+    bad = (got - ref16).abs() > 1e-2 * ref16.abs() + 1e-2 * k ** 0.5
+    assert not bad.any(), f"{int(bad.sum())} elements outside rtol 1e-2 + atol 1e-2*sqrt(K)"
+    # and no tile may hide a local fault in the global norm: worst error of every 128x256 tile
+    err = ((got - ref).abs() / k ** 0.5)
+    tiles = err.reshape(m // 128, 128, n // 256, 256).amax(dim=(1, 3))
+    assert tiles.max().item() <= 0.04, tiles.max().item()
 
 
 def test_dispatch_micro_reference_call(orc):

@@ -33,16 +33,25 @@ def pair_mode(capi, request):
                                          (2, 256, 512, 128), (4, 2048, 1024, 256)])
 def test_gemm_rs_all_ranks_on_one_gpu(capi, orc, world, M, N, K, pair_mode):
     epilogue = -1
-    A, Bt = orc.make_gemm_inputs(M, N, K, seed=0)
-    As, Bs = orc.shard_k(A, Bt, world)
-    want = orc.gemm_rs_ref(As, Bs)
     buf, views, ws = _fake_job(capi, world, M, N)
-    dA = [a.cuda() for a in As]
-    dB = [b.cuda() for b in Bs]
+    # staging area of one parity, in every rank's workspace: [world slots][tiles of the shard][64 KiB]
+    stage_bytes = world * (M // world) * ((N + 255) // 256 * 256) * 2
     for seq in (1, 2, 3):     # parity 1, 0, 1: both staging buffers and flag reuse
-        # poison the staging of this parity: nothing stale may survive into the result
+        # other inputs on every call: a partial left over from an earlier call on the same parity
+        # (a flag-epoch or parity bug) changes the answer instead of reproducing it
+        A, Bt = orc.make_gemm_inputs(M, N, K, seed=10 + seq)
+        As, Bs = orc.shard_k(A, Bt, world)
+        want = orc.gemm_rs_ref(As, Bs)
+        dA = [a.cuda() for a in As]
+        dB = [b.cuda() for b in Bs]
+        # poison outputs AND the staging buffers of the parity about to be used (bf16 0xffff = NaN):
+        # whatever is read must have been written by this call
         outs = [torch.full((M // world, N), float("nan"), dtype=torch.bfloat16, device="cuda")
                 for _ in range(world)]
+        for r in range(world):
+            stage = capi.tensor_from_ptr(ws[r] + (seq & 1) * stage_bytes, (stage_bytes,), torch.uint8)
+            stage.fill_(0xFF)
+        torch.cuda.synchronize()
         for r in range(world):
             capi.gemm_rs_phase(dA[r], dB[r], outs[r], ws[r], views[r], seq, 1, epilogue=epilogue)
         torch.cuda.synchronize()
