@@ -192,14 +192,18 @@ class GemmRs:
     metric, unit, dtype, scaling = "gemm_rs_tflops", "TFLOP/s", "bf16", "strong"
     launches_per_step = 1
 
+    @staticmethod
+    def heap_mb(P):
+        ws_mb = (2 * M_TOK * ((N_OUT + 255) // 256 * 256) * 2) // (1 << 20) + 64 if P > 1 else 0
+        return ws_mb + (M_TOK // P) * N_OUT * 2 * 2 // (1 << 20) + 64
+
     def __init__(self, ctx):
         import torch
         self.ctx = ctx
         P, rank = ctx.world, ctx.rank
         assert K_FULL % P == 0 and M_TOK % (P * 128) == 0
         self.Kloc, self.Mloc = K_FULL // P, M_TOK // P
-        ws_mb = (2 * M_TOK * ((N_OUT + 255) // 256 * 256) * 2) // (1 << 20) + 64 if P > 1 else 0
-        ctx.make_heap(ws_mb + self.Mloc * N_OUT * 2 * 2 // (1 << 20) + 64)
+        ctx.make_heap(self.heap_mb(P))
         self.shard_bytes = (M_TOK + N_OUT) * self.Kloc * 2
         self.nsets = max(2, math.ceil(256e6 / self.shard_bytes))
         g = torch.Generator(device="cuda").manual_seed(1000 + rank)
@@ -314,11 +318,12 @@ class AllReduce:
     (128 MiB); a step is one all-reduce of each."""
     metric, unit, dtype, scaling = "allreduce_busbw", "GB/s", "bf16", "weak"
     launches_per_step = 2
+    HEAP_MB = 3 * 129 + 3 * 2 + 64
 
     def __init__(self, ctx):
         import torch
         self.ctx = ctx
-        ctx.make_heap(3 * 129 + 3 * 2 + 64)
+        ctx.make_heap(self.HEAP_MB)
         # NVLS (in-switch reduction) when the system has NVLink multicast: a collective opt-in
         self.nvls = ctx.world > 1 and os.environ.get("DK_BENCH_NVLS", "1") != "0" and ctx.enable_multicast()
         g = torch.Generator(device="cuda").manual_seed(100 + ctx.rank)
@@ -408,8 +413,10 @@ class AllReduce:
 
 
 class Moe:
-    """fp8 block-scaled MoE layer: route -> permute -> (dispatch) -> quantise -> gate/up grouped
-    GEMM + SiLU*mul + requantise -> down grouped GEMM -> combine. Expert-parallel when N > 1."""
+    """fp8 block-scaled MoE layer through ONE call per step (tk_kernel.moe_layer_ep): route ->
+    exchange of the routing table -> permutation -> dispatch (once per token and GPU) -> quantise ->
+    gate/up grouped GEMM + SiLU*mul + requantise -> down grouped GEMM -> expert-side combine -> final
+    sum at home. Expert-parallel when N > 1."""
     unit, dtype, scaling = "TFLOP/s", "fp8_e4m3", "strong"
 
     SHAPES = {"moe_mixtral": dict(T=16384, H=4096, F=14336, E=8, k=2, zipf=0.0,
@@ -418,6 +425,13 @@ class Moe:
                                name="DeepSeek-V3-shaped: 32768 tokens, hidden 7168, expert inter 2048, "
                                     "E=256 top-8, Zipf(1.1)")}
 
+    @classmethod
+    def heap_mb(cls, ctx, which, tokens=0):
+        s = cls.SHAPES[which]
+        T = tokens or s["T"]
+        n = ctx.tk.moe_ep_workspace_bytes(T // ctx.world, s["k"], s["E"], s["H"], s["F"], ctx.world)
+        return n // (1 << 20) + 64
+
     def __init__(self, ctx, which, scales="fp32"):
         """scales: "fp32" = 128x128 blocks with fp32 scales, promoted in software every 128 of K (the
         format the configurations name); "pow2" = the same blocks with power-of-two scales, applied
@@ -425,6 +439,7 @@ class Moe:
         import torch
         self.ctx = ctx
         s = self.SHAPES[which]
+        self.which = which
         self.metric = which + "_tflops"
         self.scales = scales
         self.s = s
@@ -433,9 +448,7 @@ class Moe:
         assert E % P == 0 and T % P == 0
         self.epr, self.Tl = E // P, T // P
         capi = ctx.capi
-        self.cap = capi.lib().dk_moe_rows_capacity(T, k, self.epr, 128)
-        heap_mb = ((2 * self.cap * H * 2 + T * k * 4) // (1 << 20) if P > 1 else 0) + 64
-        ctx.make_heap(heap_mb)
+        ctx.make_heap(self.heap_mb(ctx, which))
         g = torch.Generator(device="cuda").manual_seed(7 + rank)
         self.x = torch.randn(self.Tl, H, device="cuda", generator=g).to(torch.bfloat16)
         logits = torch.randn(self.Tl, E, device="cuda", generator=g)
@@ -444,7 +457,7 @@ class Moe:
             p = (pi + 1.0) ** (-s["zipf"])
             logits = logits + torch.log(p / p.sum()).cuda()[None, :]
         self.logits = logits.contiguous()
-        # this rank's experts, quantised with the library's own block quantiser
+        # this rank's experts, quantised with the library's own block quantisers
         w13q, w13s, w2q, w2s = [], [], [], []
 
         def quant_w(w):
@@ -464,76 +477,116 @@ class Moe:
             del w
         self.w13q, self.w13s = torch.stack(w13q), torch.stack(w13s)
         self.w2q, self.w2s = torch.stack(w2q), torch.stack(w2s)
+        if scales == "pow2":      # block atoms of all experts, one row block after the other
+            self.w13s = self.w13s.reshape(-1, self.w13s.shape[-2], 512)
+            self.w2s = self.w2s.reshape(-1, self.w2s.shape[-2], 512)
         del w13q, w2q
-        if P > 1:   # exchange buffers live in the symmetric heap
-            self.all_idx = torch.as_tensor(ctx.iris.empty([T, k], "int32"), device="cuda")
-            self.xrecv = torch.as_tensor(ctx.iris.empty([self.cap, H]), device="cuda").view(torch.bfloat16)
-            self.ybuf = torch.as_tensor(ctx.iris.empty([self.cap, H]), device="cuda").view(torch.bfloat16)
+        nbytes = ctx.tk.moe_ep_workspace_bytes(self.Tl, k, E, H, F, P)
+        self.ws_t = ctx.iris.empty([nbytes], "uint8")           # the layer's workspace, inside the heap
+        self.ws = torch.as_tensor(self.ws_t, device="cuda")
+        self.out = torch.empty(self.Tl, H, dtype=torch.bfloat16, device="cuda")
+        self.counts = torch.zeros(self.epr, dtype=torch.int32, device="cuda")
         self.work = float(T) * k * (2.0 * H * 2 * F + 2.0 * F * H)      # useful FLOP per step, whole job
+        self.per_pair = 2.0 * H * 2 * F + 2.0 * F * H
         self.scale = 1e12
-        self.launches_per_step = 10 if P == 1 else 16
+        # route, memset, hist, scan, place, 2 slot kernels, (dispatch), quantise, 2 grouped GEMMs,
+        # combine push, final sum
+        self.launches_per_step = 12 if P == 1 else 13
         self.gemm_ms = None
-        self.pairs_here = None
+        ctx.barrier()
 
-    def step(self, i, timed_gemm=None):
-        ctx, s = self.ctx, self.s
-        capi, tk = ctx.capi, ctx.tk
-        E, k = s["E"], s["k"]
-        idx, w = tk.moe_route(self.logits, k)
-        if ctx.world == 1:
-            rop, por, offs, counts = tk.moe_permute(idx, E, 128, 0)
-            xq, xs = self._quant(self.x, por, 1, k)
-            if timed_gemm:
-                timed_gemm[0].record()
-            y = self._ffn(xq, xs, offs)
-            if timed_gemm:
-                timed_gemm[1].record()
-            out = tk.moe_combine(y, idx, rop, w, E, ctx.view)
-            self.pairs_here = counts
-        else:
-            r = ctx.rank
-            capi.allgather(idx, self.all_idx, ctx.dkview)
-            rop, por, offs, counts = tk.moe_permute(self.all_idx, E, 128, self.epr)
-            my_rop = rop[r * self.Tl:(r + 1) * self.Tl]
-            tk.moe_dispatch(self.x, idx, my_rop, self.epr, self.xrecv, ctx.view)
-            xq, xs = self._quant(self.xrecv, por[r], 2, 1)
-            if timed_gemm:
-                timed_gemm[0].record()
-            y = self._ffn(xq, xs, offs[r])
-            if timed_gemm:
-                timed_gemm[1].record()
-            self.ybuf.copy_(y)
-            out = tk.moe_combine(self.ybuf, idx, my_rop, w, self.epr, ctx.view)
-            self.pairs_here = counts[r * self.epr:(r + 1) * self.epr]
-        return out
-
-    def _quant(self, x, row_map, mode, k):
-        tk = self.ctx.tk
-        if self.scales == "pow2":
-            q, _, atoms = tk.moe_quant_pow2(x, row_map, mode, k)
-            return q, atoms
-        return tk.moe_quant(x, row_map, mode, k)
-
-    def _ffn(self, xq, xs, offs):
-        tk = self.ctx.tk
-        if self.scales == "pow2":
-            return tk.moe_ffn_mxfp8(xq, xs, self.w13q, self.w13s, self.w2q, self.w2s, offs)
-        return tk.moe_ffn_fp8(xq, xs, self.w13q, self.w13s, self.w2q, self.w2s, offs)
+    def step(self, i):
+        ctx = self.ctx
+        return ctx.tk.moe_layer_ep(self.x, self.logits, self.s["k"], self.w13q, self.w13s, self.w2q, self.w2s,
+                                   self.out, self.ws, ctx.view, 1 if self.scales == "pow2" else 0, self.counts)
 
     def time_gemm(self):
+        """The two grouped GEMMs timed inside the layer (events recorded by the call itself), median of
+        five steps; pair counts of this rank and of the most loaded rank."""
         import torch
+        ctx = self.ctx
         e = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        for ev in e:
+            ev.record()
+        torch.cuda.synchronize()
         ts = []
         for i in range(5):
-            self.step(i, e)
-            self.ctx.barrier()
+            ctx.capi.moe_ep_layer(self.x, self.logits, self.w13q, self.w13s, self.w2q, self.w2s, self.out,
+                                  self.ws.data_ptr(), ctx.dkview, self.s["k"],
+                                  scale_mode=1 if self.scales == "pow2" else 0, counts_out=self.counts,
+                                  gemm_events=e)
+            ctx.barrier()
             ts.append(e[0].elapsed_time(e[1]))
         ts.sort()
         self.gemm_ms = ts[len(ts) // 2]
-        self.pairs_rank = int(self.pairs_here.sum().item())
+        self.pairs_rank = int(self.counts.sum().item())
         # the step is timed as the max over ranks: say what the most loaded rank carried
-        self.pairs_max = int(self.ctx.max_over_ranks(float(self.pairs_rank)))
-        self.gemm_ms_max = self.ctx.max_over_ranks(self.gemm_ms)
+        self.pairs_max = int(ctx.max_over_ranks(float(self.pairs_rank)))
+        self.gemm_ms_max = ctx.max_over_ranks(self.gemm_ms)
+        self.gemm_tflops_min = -ctx.max_over_ranks(-self.pairs_rank * self.per_pair / (self.gemm_ms * 1e-3) / 1e12)
+
+    def check(self):
+        """The layer's output against the same arithmetic with NCCL as the exchange: tokens and logits
+        are all-gathered, every rank runs its own experts on ALL tokens routed to them through the
+        single-purpose entry points (route, permute, quantise, grouped GEMMs), scatters w * y into a
+        dense fp32 [T, H] buffer, and a NCCL all-reduce forms the reference. Outside the timed region;
+        relative Frobenius error of this rank's tokens, max over ranks."""
+        import torch
+        ctx, s = self.ctx, self.s
+        capi, dist = ctx.capi, ctx.dist
+        P, r, k, E, H = ctx.world, ctx.rank, s["k"], s["E"], s["H"]
+        out = self.step(0).clone()
+        torch.cuda.synchronize()
+        if P > 1:
+            xs = [torch.empty_like(self.x) for _ in range(P)]
+            ls = [torch.empty_like(self.logits) for _ in range(P)]
+            dist.all_gather(xs, self.x)
+            dist.all_gather(ls, self.logits)
+            x_all, lg_all = torch.cat(xs), torch.cat(ls)
+            del xs, ls
+        else:
+            x_all, lg_all = self.x, self.logits
+        idx, w = capi.moe_route(lg_all, k)
+        # what this rank's tokens send: one vector per (token, other GPU) after per-GPU dedup,
+        # against one per (token, expert on another GPU) without it
+        dests = (idx[r * self.Tl:(r + 1) * self.Tl] // self.epr).long()
+        onehot = torch.zeros(self.Tl, P, dtype=torch.bool, device="cuda")
+        onehot.scatter_(1, dests, True)
+        onehot[:, r] = False
+        self._vectors = int(onehot.sum().item())
+        self._remote_pairs = int((dests != r).sum().item())
+        rop, por, offs, _ = capi.moe_permute(idx, E, 128, experts_per_segment=self.epr)
+        por_me, offs_me = (por, offs) if P == 1 else (por[r].contiguous(), offs[r].contiguous())
+        cap = por_me.shape[0]
+        if self.scales == "pow2":
+            q, _, _, atoms = capi.quant_block128_pow2(x_all, rows=cap, row_map=por_me, map_mode=1, k=k)
+            y = capi.moe_ffn_mxfp8(q, atoms, self.w13q, self.w13s, self.w2q, self.w2s, offs_me)
+        else:
+            q, sc = capi.quant_block128(x_all, rows=cap, row_map=por_me, map_mode=1, k=k)
+            y = capi.moe_ffn_fp8(q, sc, self.w13q, self.w13s, self.w2q, self.w2s, offs_me)
+        del q
+        T = x_all.shape[0]
+        contrib = torch.zeros(T, H, dtype=torch.float32, device="cuda")
+        mine = (idx // self.epr) == r
+        tok = torch.arange(T, device="cuda")[:, None].expand(T, k)[mine]
+        rows, wts = rop[mine].long(), w[mine]
+        for c0 in range(0, tok.numel(), 16384):
+            sl = slice(c0, c0 + 16384)
+            contrib.index_add_(0, tok[sl], wts[sl, None] * y[rows[sl]].float())
+        del y
+        if P > 1:
+            dist.all_reduce(contrib)
+        ref = contrib[r * self.Tl:(r + 1) * self.Tl]
+        err = ((out.float() - ref).norm() / ref.norm()).item()
+        del contrib
+        return ctx.max_over_ranks(err)
+
+    def exchange_volume(self):
+        """NVLink bytes this rank's tokens cause (after check() has counted them): dispatch sends and
+        combine returns one bf16 vector per (token, other GPU)."""
+        vb = self.s["H"] * 2
+        return {"dispatch_egress_bytes_rank0": self._vectors * vb, "combine_ingress_bytes_rank0": self._vectors * vb,
+                "vectors_per_direction_rank0": self._vectors, "pairs_on_other_gpus_rank0": self._remote_pairs}
 
     def e2e_setup(self):
         import torch
@@ -552,32 +605,31 @@ class Moe:
 
     def config(self, value):
         s, P = self.s, self.ctx.world
-        per_pair = 2.0 * s["H"] * 2 * s["F"] + 2.0 * s["F"] * s["H"]
         c = {"workload": f"fp8 MoE layer, {s['name']}, 128x128 block scales "
                          f"({'power-of-two, applied by the tensor core' if self.scales == 'pow2' else 'fp32, promoted in software'}), EP={P}",
              "l2": f"expert weights ({(self.w13q.numel() + self.w2q.numel()) / 1e6:.0f} MB fp8 on this GPU) exceed L2",
              "per_gpu_tflops": value / P}
         if self.gemm_ms:
             c["grouped_gemm_ms_rank0"] = self.gemm_ms
-            c["grouped_gemm_tflops_rank0"] = self.pairs_rank * per_pair / (self.gemm_ms * 1e-3) / 1e12
+            c["grouped_gemm_tflops_rank0"] = self.pairs_rank * self.per_pair / (self.gemm_ms * 1e-3) / 1e12
             c["pairs_rank0"] = self.pairs_rank
             c["pairs_max_rank"] = self.pairs_max
             c["grouped_gemm_ms_max_rank"] = self.gemm_ms_max
         return c
 
     def roofline(self, ms_step, sustained, peaks, peak_src):
-        s = self.s
-        per_pair = 2.0 * s["H"] * 2 * s["F"] + 2.0 * s["F"] * s["H"]
         bf16 = peaks.get("bf16_tflops_sustained" if sustained else "bf16_tflops")
         peak = 2.0 * bf16 if bf16 else None          # no measured fp8 figure: twice the measured bf16 GEMM
         if self.gemm_ms:
-            ach = self.pairs_rank * per_pair / (self.gemm_ms * 1e-3) / 1e12
+            ach = self.pairs_rank * self.per_pair / (self.gemm_ms * 1e-3) / 1e12
             what = "grouped GEMM kernels alone (rank 0)"
         else:
             ach = (self.work / self.ctx.world) / (ms_step * 1e-3) / 1e12
             what = "whole step"
         return {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
-                "frac": ach / peak if peak else None, "traffic": load_traffic(self.metric + ("_pow2" if self.scales == "pow2" else "")), "of": what,
+                "frac": ach / peak if peak else None,
+                "frac_of_nominal_4500": ach / 4500.0,
+                "traffic": load_traffic(self.metric + ("_pow2" if self.scales == "pow2" else "")), "of": what,
                 "peak_source": f"2 x {peak_src} cuBLAS bf16 ({'sustained' if sustained else 'burst'}) "
                                f"taken as the fp8 dense peak"}
 
@@ -595,6 +647,10 @@ class Ctx:
         self.iris = None
 
     def make_heap(self, mb):
+        """The symmetric heap of this process, created on the first call (later calls reuse it: blocks
+        return to it when the tensors that own them die)."""
+        if self.iris is not None:
+            return
         self.iris = self.iris_py.Iris(heap_size_mb=int(mb), verbose=False)
         assert self.iris.rank() == self.rank and self.iris.world_size() == self.world
         self.view = self.iris.get_device_view()
@@ -630,6 +686,77 @@ def _claim_stdout():
     return real
 
 
+def time_steps(ctx, wl, steps, warmup):
+    """W untimed steps, then K steps between CUDA events, barrier + synchronize on both sides.
+    Returns (milliseconds per step as the max over ranks, wall-clock interval of the timed region)."""
+    import torch
+    ctx.barrier()
+    for i in range(warmup):
+        wl.step(i)
+    ctx.barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    ev0.record()
+    for i in range(steps):
+        wl.step(i)
+    ev1.record()
+    ctx.barrier()
+    return ctx.max_over_ranks(ev0.elapsed_time(ev1)) / steps, (t0, time.time())
+
+
+def moe_secondary(ctx, which, scales, peaks, tokens=0):
+    """One MoE configuration at the launched number of GPUs: step time, the grouped GEMMs timed inside
+    the step, the share of the step that is not GEMM, the exchange volume, and a parity check."""
+    if tokens:
+        Moe.SHAPES[which] = dict(Moe.SHAPES[which], T=tokens)
+    wl = Moe(ctx, which, scales)
+    ms, _ = time_steps(ctx, wl, steps=10, warmup=3)
+    wl.time_gemm()
+    err = wl.check()
+    P = ctx.world
+    tf_job = wl.work / (ms * 1e-3) / 1e12
+    gemm_tf = wl.pairs_rank * wl.per_pair / (wl.gemm_ms * 1e-3) / 1e12
+    burst, sust = peaks.get("bf16_tflops"), peaks.get("bf16_tflops_sustained")
+    e = {"workload": wl.config(tf_job)["workload"], "step_ms": ms, "tflops_whole_job": tf_job,
+         "tflops_per_gpu": tf_job / P,
+         "grouped_gemm_tflops_per_gpu_rank0": gemm_tf,
+         "grouped_gemm_tflops_per_gpu_slowest_rank": wl.gemm_tflops_min,
+         "grouped_gemm_ms_rank0": wl.gemm_ms, "grouped_gemm_ms_max_rank": wl.gemm_ms_max,
+         "roofline_frac_of_2x_measured_bf16_burst": gemm_tf / (2 * burst) if burst else None,
+         "roofline_frac_of_2x_measured_bf16_sustained": gemm_tf / (2 * sust) if sust else None,
+         "roofline_frac_of_nominal_4500": gemm_tf / 4500.0,
+         "non_gemm_share_of_step": max(0.0, 1.0 - wl.gemm_ms_max / ms),
+         "pairs_rank0": wl.pairs_rank, "pairs_max_rank": wl.pairs_max,
+         "traffic": load_traffic(wl.metric + ("_pow2" if scales == "pow2" else "")),
+         "check_rel_fro": err}
+    e.update(wl.exchange_volume())
+    assert err <= 2e-2, f"{which} ({scales}): layer differs from the NCCL-exchanged reference by {err}"
+    del wl
+    import gc
+    import torch
+    gc.collect()
+    torch.cuda.empty_cache()
+    return e
+
+
+def allreduce_secondary(ctx):
+    wl = AllReduce(ctx)
+    ms, _ = time_steps(ctx, wl, steps=10, warmup=3)
+    wl.time_each()
+    err = wl.check()
+    P = ctx.world
+    e = {"nvls": bool(wl.nvls), "check_rel_fro": err, "step_busbw_gbs": wl.work / (ms * 1e-3) / 1e9}
+    for name, nbytes in (("decode", 64 * 8192 * 2), ("prefill", 8192 * 8192 * 2)):
+        for an in ("oneshot", "twoshot", "nvls"):
+            us = wl.detail.get(f"{name}_{an}_us")
+            if us is not None:
+                e[f"{name}_{an}_us"] = us
+                e[f"{name}_{an}_busbw_gbs"] = nbytes * 2.0 * (P - 1) / P / (us * 1e-6) / 1e9
+    assert err <= 1e-2, f"all-reduce differs from the NCCL sum by {err}"
+    del wl
+    return e
+
+
 def main():
     out = _claim_stdout()
     ap = argparse.ArgumentParser()
@@ -645,9 +772,12 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="skip the other operators of the metric (MoE layers, all-reduce, sustained GEMM)")
     ap.add_argument("--shape", default=None, help="M,N,K override of the GEMM workload (profiling runs)")
     ap.add_argument("--check", action="store_true",
-                    help="also compare one result with a NCCL/torch sum (outside the timed region)")
+                    help="compare one result with a NCCL/torch reference outside the timed region "
+                         "(always done when more than one GPU is used)")
     ap.add_argument("--tokens", type=int, default=0, help="token-count override of a MoE workload (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 0)
@@ -673,6 +803,14 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     ctx = Ctx(rank, world, local_rank)
+    secondary_on = args.workload == "gemm_rs" and not args.no_secondary and not args.shape
+    # one symmetric heap for everything this run will do
+    need = {"gemm_rs": GemmRs.heap_mb(world), "allreduce": AllReduce.HEAP_MB}
+    for wname in ("moe_mixtral", "moe_dsv3"):
+        need[wname] = Moe.heap_mb(ctx, wname, args.tokens if args.workload == wname else 0)
+    heap_mb = need[args.workload] + (sum(v for k_, v in need.items() if k_ != args.workload) if secondary_on else 0)
+    ctx.make_heap(heap_mb)
+
     if args.workload == "gemm_rs":
         wl = GemmRs(ctx)
     elif args.workload == "allreduce":
@@ -689,18 +827,7 @@ def main():
         t_wait = time.time() + 8.0
         while not sampler.lines and time.time() < t_wait:   # let nvidia-smi finish starting up
             time.sleep(0.05)
-    barrier()
-    for i in range(args.warmup):
-        wl.step(i)
-    barrier()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t_clock0 = time.time()
-    ev0.record()
-    for i in range(args.steps):
-        wl.step(i)
-    ev1.record()
-    barrier()
-    ms_total = ev0.elapsed_time(ev1)
+    ms_step, (t_clock0, _) = time_steps(ctx, wl, args.steps, args.warmup)
     clocks_extended = False
     if sampler and sampler.count_in(t_clock0, time.time()) < 4:
         # the timed region was shorter than a few sampling periods: keep the same load running,
@@ -725,17 +852,24 @@ def main():
     if clocks is not None:
         clocks["extended_by_untimed_steps"] = extra if clocks_extended else 0
     status = ctx.tk.device_status()
-    assert status[0] == 0, f"device-side wait timed out: {status}"
-    ms_step = ctx.max_over_ranks(ms_total) / args.steps
+    assert status[0] == 0, f"device-side error record: {status}"
     value = wl.work / (ms_step * 1e-3) / wl.scale
 
+    # parity outside the timed region: always when peers are involved
     check_err = None
-    if args.check and hasattr(wl, "check"):
+    if args.check or world > 1:
         check_err = wl.check()
     if isinstance(wl, AllReduce):
         wl.time_each()
     if isinstance(wl, Moe):
         wl.time_gemm()
+
+    # the same step back to back for at least two seconds: the figure a long-running job sees under
+    # the power cap, against the sustained peak
+    sustained_ms = None
+    if isinstance(wl, GemmRs) and secondary_on:
+        n = max(args.steps, int(math.ceil(2000.0 / ms_step)))
+        sustained_ms, _ = time_steps(ctx, wl, n, 0)
 
     e2e_value = e2e_ms = None
     h2d = d2h = 0
@@ -755,10 +889,11 @@ def main():
             e2e_ms = ctx.max_over_ranks(e0.elapsed_time(e1)) / args.e2e_steps
             e2e_value = wl.work / (e2e_ms * 1e-3) / wl.scale
     status = ctx.tk.device_status()
-    assert status[0] == 0, f"device-side wait timed out: {status}"
+    assert status[0] == 0, f"device-side error record: {status}"
 
+    peaks, peak_src = load_peaks()
+    line = None
     if rank == 0:
-        peaks, peak_src = load_peaks()
         sustained = ms_step * args.steps * 1e-3 >= 1.0
         line = {
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world,
@@ -774,14 +909,44 @@ def main():
         }
         if check_err is not None:
             line["check_rel_fro"] = check_err
+        if sustained_ms is not None:
+            r = wl.roofline(sustained_ms, True, peaks, peak_src)
+            line["roofline"]["sustained"] = {"ms_per_step": sustained_ms, "achieved": r["achieved"], "peak": r["peak"],
+                                             "frac": r["frac"], "peak_source": r["peak_source"],
+                                             "seconds": sustained_ms * max(args.steps, int(math.ceil(2000.0 / ms_step))) * 1e-3}
         if world == 1 and not args.no_cpu_baseline and isinstance(wl, GemmRs):
             tf, threads, desc, dt = cpu_reference_tflops()
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
                                     "sample": desc, "seconds": dt}
+    if check_err is not None and isinstance(wl, GemmRs):
+        assert check_err <= 1e-2, f"GEMM + reduce-scatter differs from the NCCL sum by {check_err}"
+
+    # the other operators the metric names, at the same number of GPUs
+    if secondary_on:
+        del wl
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        sec = {}
+        if world > 1:
+            sec["allreduce"] = allreduce_secondary(ctx)
+        for which in ("moe_mixtral", "moe_dsv3"):
+            for scales in ("fp32", "pow2"):
+                sec[f"{which}_{scales}"] = moe_secondary(ctx, which, scales, peaks)
+        if world == 1:
+            sys.path.insert(0, str(ROOT / "examples"))
+            import bench_gemm
+            sec["gemm_reference_bench_shapes"] = bench_gemm.run(iters=20)
+        status = ctx.tk.device_status()
+        assert status[0] == 0, f"device-side error record: {status}"
+        if line is not None:
+            line["secondary"] = sec
+    else:
+        del wl
+    if rank == 0:
         out.write(json.dumps(line) + "\n")
         out.flush()
     barrier()
-    del wl
     ctx.view = ctx.dkview = None
     ctx.iris = None
     if world > 1:

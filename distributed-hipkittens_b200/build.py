@@ -28,7 +28,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-r
               "-cudart", "static"]
 
 CUDA_SOURCES = ["dk_host.cu", "dk_gemm.cu", "dk_allreduce.cu", "dk_moe.cu", "dk_mx.cu",
-                "dk_moe_gemm.cu", "dk_moe_ep.cu", "dk_heap.cu"]
+                "dk_moe_gemm.cu", "dk_moe_ep.cu", "dk_moe_layer.cu", "dk_heap.cu"]
 CPP_SOURCES = ["dk_comm.cpp"]
 PYBIND_MODULES = {"iris_py": "iris_py.cpp", "tk_kernel": "tk_kernel.cpp"}
 

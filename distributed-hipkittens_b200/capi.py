@@ -27,6 +27,18 @@ class DkView(C.Structure):
     ]
 
 
+class DkMoeEpArgs(C.Structure):
+    """Mirror of `dk_moe_ep_args`."""
+    _fields_ = [
+        ("T_loc", C.c_int), ("k", C.c_int), ("E", C.c_int), ("H", C.c_int), ("F", C.c_int),
+        ("scale_mode", C.c_int),
+        ("x", C.c_void_p), ("logits", C.c_void_p),
+        ("w13q", C.c_void_p), ("w13s", C.c_void_p), ("w2q", C.c_void_p), ("w2s", C.c_void_p),
+        ("out", C.c_void_p), ("workspace", C.c_void_p), ("counts_out", C.c_void_p),
+        ("ev_gemm_begin", C.c_void_p), ("ev_gemm_end", C.c_void_p),
+    ]
+
+
 class DkError(RuntimeError):
     def __init__(self, code: int, what: str, detail: str):
         super().__init__(f"{what}: {detail}" if detail else what)
@@ -77,6 +89,7 @@ def _declare(L: C.CDLL) -> None:
     L.dk_gemm_rs_workspace_bytes.restype = sz
     L.dk_gemm_rs_workspace_bytes.argtypes = [i, i, i]
     L.dk_gemm_rs_workspace_init.argtypes = [vp, sz, C.POINTER(DkView), vp]
+    L.dk_gemm_rs_workspace_get.argtypes = [C.POINTER(DkView), i, i, vp, C.POINTER(vp)]
     L.dk_gemm_rs.argtypes = [vp, vp, vp, i, i, i, vp, C.POINTER(DkView), vp]
     L.dk_gemm_rs_phase.argtypes = [vp, vp, vp, i, i, i, vp, C.POINTER(DkView), C.c_uint, i, i, vp]
     L.dk_allreduce.argtypes = [vp, vp, sz, i, C.POINTER(DkView), vp]
@@ -100,6 +113,9 @@ def _declare(L: C.CDLL) -> None:
     L.dk_gemm_mxfp8.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, vp]
     L.dk_quant_block128_pow2.argtypes = [vp, i, i, vp, i, i, vp, vp, vp, vp, vp]
     L.dk_moe_grouped_gemm_mxfp8.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, vp, vp, vp, vp]
+    L.dk_moe_ep_workspace_bytes.restype = sz
+    L.dk_moe_ep_workspace_bytes.argtypes = [i, i, i, i, i, i]
+    L.dk_moe_ep_layer.argtypes = [C.POINTER(DkMoeEpArgs), C.POINTER(DkView), C.c_uint, i, vp]
     L.dk_peer_barrier.argtypes = [C.POINTER(DkView), vp]
     L.dk_peer_barrier_epoch.argtypes = [C.POINTER(DkView), C.c_uint, vp]
     L.dk_set_peer_wait_ms.argtypes = [i]
@@ -462,6 +478,33 @@ def moe_ffn_mxfp8(xq, x_atoms, w13q, w13_atoms, w2q, w2_atoms, offsets, stream=N
 
 
 # ---------------------------------------------------------------------------- expert parallel
+def moe_ep_workspace_bytes(T_loc: int, k: int, E: int, H: int, F: int, world: int) -> int:
+    return lib().dk_moe_ep_workspace_bytes(T_loc, k, E, H, F, world)
+
+
+def moe_ep_layer(x, logits, w13q, w13s, w2q, w2s, out, workspace_ptr: int, view, k: int, scale_mode: int = 0,
+                 epoch: int = 0, phases: int = 15, counts_out=None, gemm_events=None, stream=None):
+    """One expert-parallel MoE layer (dk_moe_ep_layer). `workspace_ptr` addresses
+    moe_ep_workspace_bytes(...) bytes (inside the heap when the view has more than one rank)."""
+    _need_cuda(x, logits, w13q, w13s, w2q, w2s, out)
+    a = DkMoeEpArgs()
+    a.T_loc, a.H = x.shape
+    a.E = logits.shape[1]
+    a.k = k
+    a.F = w2q.shape[2]
+    a.scale_mode = scale_mode
+    a.x, a.logits = x.data_ptr(), logits.data_ptr()
+    a.w13q, a.w13s, a.w2q, a.w2s = w13q.data_ptr(), w13s.data_ptr(), w2q.data_ptr(), w2s.data_ptr()
+    a.out = out.data_ptr()
+    a.workspace = workspace_ptr
+    a.counts_out = counts_out.data_ptr() if counts_out is not None else None
+    if gemm_events is not None:      # two torch.cuda.Event(enable_timing=True) that have been recorded once
+        a.ev_gemm_begin, a.ev_gemm_end = gemm_events[0].cuda_event, gemm_events[1].cuda_event
+    check(lib().dk_moe_ep_layer(C.byref(a), C.byref(view) if view is not None else None, epoch, phases,
+                                _stream_ptr(stream)))
+    return out
+
+
 def peer_barrier(view: DkView, stream=None):
     check(lib().dk_peer_barrier(C.byref(view), _stream_ptr(stream)))
 

@@ -808,6 +808,36 @@ extern "C" int dk_gemm_rs_workspace_init(void* workspace, size_t bytes, const dk
     return DK_OK;
 }
 
+extern "C" int dk_gemm_rs_workspace_get(const dk_view* view, int M, int N, void* stream, void** out) {
+    DK_REQUIRE(out != nullptr, "null result pointer");
+    *out = nullptr;
+    if (view == nullptr || view->world <= 1) return DK_OK;
+    dk_heap* h = static_cast<dk_heap*>(view->heap);
+    DK_REQUIRE(h != nullptr, "view has no heap handle");
+    DK_REQUIRE(M > 0 && N > 0 && M % (view->world * dk::BM) == 0, "M must be a positive multiple of world * 128");
+    {
+        std::lock_guard<std::mutex> lk(h->mu);
+        auto it = h->rs_ws.find({M, N});
+        if (it != h->rs_ws.end()) {
+            *out = it->second;
+            return DK_OK;
+        }
+    }
+    const size_t bytes = dk::gemm_rs_workspace_bytes(M, N, view->world);
+    void* ws = dk_heap_alloc(h, bytes, 1024);
+    if (ws == nullptr) {
+        dk::set_last_error("symmetric heap exhausted: a reduce-scatter workspace of " + std::to_string(bytes) +
+                           " bytes does not fit");
+        return DK_ERR_NOMEM;
+    }
+    const int rc = dk_gemm_rs_workspace_init(ws, bytes, view, stream);
+    if (rc != DK_OK) return rc;
+    std::lock_guard<std::mutex> lk(h->mu);
+    h->rs_ws[{M, N}] = ws;
+    *out = ws;
+    return DK_OK;
+}
+
 extern "C" int dk_gemm_rs_phase(const void* A, const void* Bt, void* out, int M, int N, int Kloc,
                                 void* workspace, const dk_view* view, unsigned seq, int phases,
                                 int epilogue, void* stream) {

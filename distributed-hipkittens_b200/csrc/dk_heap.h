@@ -4,6 +4,7 @@
 
 #include <map>
 #include <mutex>
+#include <utility>
 
 #include "../../include/dk_b200.h"
 
@@ -40,6 +41,7 @@ struct dk_heap {
     std::map<size_t, size_t> free_blocks;  // offset -> size, coalesced
     std::map<size_t, size_t> used_blocks;  // offset -> size
     std::map<void*, unsigned> rs_seq;      // per GEMM+RS workspace: calls made so far
+    std::map<std::pair<int, int>, void*> rs_ws;  // workspaces the heap owns, by (M, N); they die with it
 };
 
 namespace dk {

@@ -18,9 +18,7 @@
 #include <mutex>
 #include <string>
 
-#include "dk_heap.h"
-#include "dk_host.h"
-#include "dk_ptx.cuh"
+#include "dk_moe_int.h"
 
 namespace dk {
 
@@ -30,11 +28,10 @@ constexpr int ROUTE_MAX_K = 8;
 
 // One warp per token. Lane l holds experts l, l+32, ... (E <= 256 -> at most 8 per lane).
 __global__ void __launch_bounds__(256) moe_route_kernel(const float* __restrict__ logits, int T, int E,
-                                                        int k, int* __restrict__ topk_idx,
-                                                        float* __restrict__ topk_w) {
+                                                        int k, const RouteOut out, const EpSignal sig) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
-    if (warp >= T) return;
+    if (warp < T) {
     const float* row = logits + static_cast<size_t>(warp) * E;
     float v[ROUTE_MAX_E / 32];
     bool taken[ROUTE_MAX_E / 32];
@@ -89,10 +86,16 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float* __restrict_
             sum += p[j];
         }
         for (int j = 0; j < k; ++j) {
-            topk_idx[static_cast<size_t>(warp) * k + j] = sel_e[j];
-            topk_w[static_cast<size_t>(warp) * k + j] = p[j] / sum;
+            const size_t at = static_cast<size_t>(out.row_base + warp) * k + j;
+            const float wj = p[j] / sum;
+            for (int r = 0; r < out.n_out; ++r) {
+                out.idx[r][at] = sel_e[j];
+                out.w[r][at] = wj;
+            }
         }
     }
+    }
+    ep_signal_done(sig);
 }
 
 // ------------------------------------------------------------------------------------ permute
@@ -102,15 +105,24 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float* __restrict_
 //   C  position of every pair = offset[e] + pairs of e in earlier chunks + earlier pairs of e in
 //      this chunk (warp match + per-warp counts)
 constexpr int PERM_CHUNK = 1024;  // pairs per block, one per thread
+// sites of the bad-index record (DK_DEV_BAD_INDEX): an expert id outside [0, E) in topk_idx (the pair
+// is left out: row_of_pair = -1), a row at or beyond the caller's capacity (the pair is left out)
+enum : unsigned { SITE_PERM_EXPERT = 80, SITE_PERM_ROW = 81 };
 
 __global__ void __launch_bounds__(PERM_CHUNK) moe_hist_kernel(const int* __restrict__ topk_idx,
                                                               int npairs, int E,
-                                                              int* __restrict__ chunk_counts) {
+                                                              int* __restrict__ chunk_counts,
+                                                              unsigned* status, const EpWait wait) {
     __shared__ int cnt[ROUTE_MAX_E];
+    if (!ep_wait_sources(wait)) return;
     for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
     __syncthreads();
     const int i = blockIdx.x * PERM_CHUNK + threadIdx.x;
-    if (i < npairs) atomicAdd(&cnt[topk_idx[i]], 1);  // a count: order-independent
+    if (i < npairs) {
+        const int e = topk_idx[i];
+        if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);  // a count: order-independent
+        else record_bad_index(status, SITE_PERM_EXPERT, static_cast<unsigned>(i));
+    }
     __syncthreads();
     for (int e = threadIdx.x; e < E; e += blockDim.x) chunk_counts[static_cast<size_t>(blockIdx.x) * E + e] = cnt[e];
 }
@@ -153,15 +165,20 @@ __global__ void __launch_bounds__(PERM_CHUNK) moe_place_kernel(const int* __rest
                                                                const int* __restrict__ offsets,
                                                                int* __restrict__ row_of_pair,
                                                                int* __restrict__ pair_of_row,
-                                                               int seg_row_capacity) {
+                                                               int seg_row_capacity, unsigned* status) {
     __shared__ int warp_cnt[PERM_CHUNK / 32][ROUTE_MAX_E];  // 32 KiB
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int x = threadIdx.x; x < (PERM_CHUNK / 32) * ROUTE_MAX_E; x += blockDim.x)
         (&warp_cnt[0][0])[x] = 0;
     __syncthreads();
     const int i = blockIdx.x * PERM_CHUNK + threadIdx.x;
-    const bool live = i < npairs;
-    const int e = live ? topk_idx[i] : -1;
+    bool live = i < npairs;
+    int e = live ? topk_idx[i] : -1;
+    if (live && (e < 0 || e >= E)) {  // recorded by the histogram kernel; the pair gets no row
+        row_of_pair[i] = -1;
+        live = false;
+        e = -1;
+    }
     // lanes of this warp holding the same expert; my rank among them = those before me
     const unsigned peers = __match_any_sync(0xffffffffu, e);
     const int rank_in_warp = __popc(peers & ((1u << lane) - 1));
@@ -173,8 +190,13 @@ __global__ void __launch_bounds__(PERM_CHUNK) moe_place_kernel(const int* __rest
         const int g = e / seg;
         const int row = offsets[g * (seg + 1) + (e - g * seg)] +
                         chunk_base[static_cast<size_t>(blockIdx.x) * E + e] + before + rank_in_warp;
-        row_of_pair[i] = row;
-        pair_of_row[static_cast<size_t>(g) * seg_row_capacity + row] = i;
+        if (row < seg_row_capacity) {
+            row_of_pair[i] = row;
+            pair_of_row[static_cast<size_t>(g) * seg_row_capacity + row] = i;
+        } else {
+            row_of_pair[i] = -1;
+            record_bad_index(status, SITE_PERM_ROW, static_cast<unsigned>(i));
+        }
     }
 }
 
@@ -183,6 +205,9 @@ __global__ void __launch_bounds__(PERM_CHUNK) moe_place_kernel(const int* __rest
 // t/16 + 16*i, i = 0..7. Source rows come straight from x, or through a row map:
 //   map_mode 0: row r of x;  1: row map[r] / k of x (gather), zeros where map[r] < 0;
 //   2: row r of x where map[r] >= 0, zeros elsewhere (rows already in place, padding undefined)
+//   3: row map2[map[r] / k] of x (a gather through two maps: pair of the row -> token -> where the
+//      token's vector landed), zeros where either entry is negative
+// row_limit (device memory, may be null): row blocks at or beyond *row_limit are not produced.
 // POW2: the scale is rounded UP to a power of two, s = 2^ceil(log2(amax/448)) (1 for an all-zero
 // block), and also written as an e8m0 byte (log2(s) + 127) and into the scale atoms the
 // block-scaled tensor-core path reads: per 128 rows and four column blocks one 512-byte atom whose
@@ -192,9 +217,13 @@ __global__ void __launch_bounds__(256) quant_block128_kernel(const __nv_bfloat16
                                                              const int* __restrict__ map, int map_mode,
                                                              int k, uint8_t* __restrict__ q,
                                                              float* __restrict__ s, uint8_t* __restrict__ e8,
-                                                             uint8_t* __restrict__ atoms) {
+                                                             uint8_t* __restrict__ atoms,
+                                                             const int* __restrict__ map2,
+                                                             const int* __restrict__ row_limit, const EpWait wait) {
     __shared__ float red[8];
     const int bc = blockIdx.x, br = blockIdx.y;
+    if (row_limit != nullptr && br * 128 >= *row_limit) return;
+    if (!ep_wait_sources(wait)) return;
     const int cchunk = (threadIdx.x & 15) * 8;
     const int r0 = threadIdx.x >> 4;
     float vals[8][8];
@@ -208,6 +237,11 @@ __global__ void __launch_bounds__(256) quant_block128_kernel(const __nv_bfloat16
             const int mv = map[r];
             valid = mv >= 0;
             if (map_mode == 1) src = valid ? mv / k : 0;
+            if (map_mode == 3) {
+                const int slot = valid ? map2[mv / k] : -1;
+                valid = slot >= 0;
+                src = valid ? slot : 0;
+            }
         }
         uint4 u = make_uint4(0, 0, 0, 0);
         if (valid) u = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(src) * C + bc * 128 + cchunk);
@@ -287,6 +321,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const CombineArgs a) {
     for (int c = threadIdx.x * 8; c < a.H; c += blockDim.x * 8) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         for (int j = 0; j < a.k; ++j) {
+            if (row_s[j] < 0) continue;  // a pair the permutation left out (bad expert id / no room)
             const uint4 u = __ldcg(reinterpret_cast<const uint4*>(
                 a.y[dst_s[j]] + static_cast<size_t>(row_s[j]) * a.H + c));
             const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
@@ -307,23 +342,36 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const CombineArgs a) {
     }
 }
 
+int moe_route_launch(const float* logits, int T, int E, int k, const RouteOut& out, const EpSignal& sig,
+                     cudaStream_t st) {
+    const int warps_per_block = 8;
+    int blocks = (T + warps_per_block - 1) / warps_per_block;
+    if (blocks < 1) blocks = 1;  // a launch with a signal must run even without tokens
+    moe_route_kernel<<<blocks, warps_per_block * 32, 0, st>>>(logits, T, E, k, out, sig);
+    DK_CUDA_OK(cudaGetLastError());
+    return DK_OK;
+}
+
 // shared by the allocating and the non-allocating permute entry points
 int moe_permute_launch(const int* topk_idx, int T, int k, int E, int pad, int seg, int* row_of_pair,
                        int* pair_of_row, int seg_row_capacity, int* offsets, int* counts,
-                       int* scratch, cudaStream_t st) {
+                       int* scratch, const EpWait& wait, cudaStream_t st) {
     const int npairs = T * k;
     const int nseg = E / seg;
+    unsigned* status = nullptr;
+    const int src = device_status_ptr(&status);
+    if (src != DK_OK) return src;
     DK_CUDA_OK(cudaMemsetAsync(pair_of_row, 0xff, static_cast<size_t>(nseg) * seg_row_capacity * sizeof(int), st));
     const int nchunks = (npairs + PERM_CHUNK - 1) / PERM_CHUNK;
     if (nchunks > 0) {
-        moe_hist_kernel<<<nchunks, PERM_CHUNK, 0, st>>>(topk_idx, npairs, E, scratch);
+        moe_hist_kernel<<<nchunks, PERM_CHUNK, 0, st>>>(topk_idx, npairs, E, scratch, status, wait);
         DK_CUDA_OK(cudaGetLastError());
     }
     moe_scan_kernel<<<1, ROUTE_MAX_E, 0, st>>>(scratch, nchunks, E, pad, seg, counts, offsets);
     DK_CUDA_OK(cudaGetLastError());
     if (nchunks > 0) {
         moe_place_kernel<<<nchunks, PERM_CHUNK, 0, st>>>(topk_idx, npairs, E, seg, scratch, offsets,
-                                                         row_of_pair, pair_of_row, seg_row_capacity);
+                                                         row_of_pair, pair_of_row, seg_row_capacity, status);
         DK_CUDA_OK(cudaGetLastError());
     }
     return DK_OK;
@@ -341,6 +389,30 @@ int moe_permute_check(const void* topk_idx, int T, int k, int E, int pad, int se
     return DK_OK;
 }
 
+int quant_block128_launch(const void* x, int R, int C, const int* map, int map_mode, int k, const int* map2,
+                          const int* row_limit, void* q, float* s, void* e8, void* atoms, bool pow2,
+                          const EpWait& wait, cudaStream_t st) {
+    DK_REQUIRE(R >= 0 && C > 0 && R % 128 == 0 && C % 128 == 0, "R and C must be multiples of 128");
+    DK_REQUIRE(map_mode >= 0 && map_mode <= 3, "map_mode must be 0..3");
+    DK_REQUIRE(map_mode == 0 || map != nullptr, "row_map is null");
+    DK_REQUIRE((map_mode != 1 && map_mode != 3) || k >= 1, "k must be positive");
+    DK_REQUIRE(map_mode != 3 || map2 != nullptr, "second map is null");
+    if (R == 0) return DK_OK;
+    DK_REQUIRE(x && q, "null buffer");
+    DK_REQUIRE(!pow2 || (reinterpret_cast<uintptr_t>(atoms) & 15) == 0, "the scale atoms must be 16-byte aligned");
+    const dim3 grid(C / 128, R / 128);
+    if (pow2)
+        quant_block128_kernel<true><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), R, C, map, map_mode, k,
+                                                          static_cast<uint8_t*>(q), s, static_cast<uint8_t*>(e8),
+                                                          static_cast<uint8_t*>(atoms), map2, row_limit, wait);
+    else
+        quant_block128_kernel<false><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), R, C, map, map_mode,
+                                                           k, static_cast<uint8_t*>(q), s, nullptr, nullptr, map2,
+                                                           row_limit, wait);
+    DK_CUDA_OK(cudaGetLastError());
+    return DK_OK;
+}
+
 }  // namespace dk
 
 extern "C" {
@@ -351,11 +423,12 @@ int dk_moe_route(const float* logits, int T, int E, int k, int* topk_idx, float*
     DK_REQUIRE(k >= 1 && k <= ROUTE_MAX_K && k <= E, "k must be 1..8 and <= E");
     if (T == 0) return DK_OK;
     DK_REQUIRE(logits && topk_idx && topk_w, "null buffer");
-    const int warps_per_block = 8;
-    moe_route_kernel<<<(T + warps_per_block - 1) / warps_per_block, warps_per_block * 32, 0,
-                       static_cast<cudaStream_t>(stream)>>>(logits, T, E, k, topk_idx, topk_w);
-    DK_CUDA_OK(cudaGetLastError());
-    return DK_OK;
+    RouteOut out{};
+    out.idx[0] = topk_idx;
+    out.w[0] = topk_w;
+    out.n_out = 1;
+    out.row_base = 0;
+    return moe_route_launch(logits, T, E, k, out, EpSignal{}, static_cast<cudaStream_t>(stream));
 }
 
 size_t dk_moe_permute_scratch_bytes(int T, int k, int E) {
@@ -381,7 +454,7 @@ int dk_moe_permute(const int* topk_idx, int T, int k, int E, int pad, int expert
     DK_REQUIRE(scratch != nullptr && scratch_bytes >= dk_moe_permute_scratch_bytes(T, k, E),
                "scratch too small: see dk_moe_permute_scratch_bytes");
     return moe_permute_launch(topk_idx, T, k, E, pad, experts_per_segment, row_of_pair, pair_of_row,
-                              seg_row_capacity, offsets, counts, static_cast<int*>(scratch),
+                              seg_row_capacity, offsets, counts, static_cast<int*>(scratch), EpWait{},
                               static_cast<cudaStream_t>(stream));
 }
 
@@ -428,41 +501,26 @@ int dk_moe_permute_static(const int* topk_idx, int T, int k, int E, int pad, int
     // Nothing has to be cleared: the histogram kernel writes every [chunk][expert] entry this call
     // reads, so whatever an earlier call left behind is overwritten before use.
     return moe_permute_launch(topk_idx, T, k, E, pad, experts_per_segment, row_of_pair, pair_of_row,
-                              seg_row_capacity, offsets, counts, scratch,
+                              seg_row_capacity, offsets, counts, scratch, EpWait{},
                               static_cast<cudaStream_t>(stream));
 }
 
 int dk_quant_block128(const void* x, int R, int C, const int* row_map, int map_mode, int k, void* q,
                       float* s, void* stream) {
     using namespace dk;
-    DK_REQUIRE(R >= 0 && C > 0 && R % 128 == 0 && C % 128 == 0, "R and C must be multiples of 128");
     DK_REQUIRE(map_mode >= 0 && map_mode <= 2, "map_mode must be 0, 1 or 2");
-    DK_REQUIRE(map_mode == 0 || row_map != nullptr, "row_map is null");
-    DK_REQUIRE(map_mode != 1 || k >= 1, "k must be positive");
-    if (R == 0) return DK_OK;
-    DK_REQUIRE(x && q && s, "null buffer");
-    quant_block128_kernel<false><<<dim3(C / 128, R / 128), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(x), R, C, row_map, map_mode, k, static_cast<uint8_t*>(q), s, nullptr,
-        nullptr);
-    DK_CUDA_OK(cudaGetLastError());
-    return DK_OK;
+    DK_REQUIRE(R == 0 || s != nullptr, "null buffer");
+    return quant_block128_launch(x, R, C, row_map, map_mode, k, nullptr, nullptr, q, s, nullptr, nullptr, false,
+                                 EpWait{}, static_cast<cudaStream_t>(stream));
 }
 
 int dk_quant_block128_pow2(const void* x, int R, int C, const int* row_map, int map_mode, int k, void* q,
                            float* s, void* e8, void* sf_atoms, void* stream) {
     using namespace dk;
-    DK_REQUIRE(R >= 0 && C > 0 && R % 128 == 0 && C % 128 == 0, "R and C must be multiples of 128");
     DK_REQUIRE(map_mode >= 0 && map_mode <= 2, "map_mode must be 0, 1 or 2");
-    DK_REQUIRE(map_mode == 0 || row_map != nullptr, "row_map is null");
-    DK_REQUIRE(map_mode != 1 || k >= 1, "k must be positive");
-    if (R == 0) return DK_OK;
-    DK_REQUIRE(x && q && sf_atoms, "null buffer");
-    DK_REQUIRE((reinterpret_cast<uintptr_t>(sf_atoms) & 15) == 0, "the scale atoms must be 16-byte aligned");
-    quant_block128_kernel<true><<<dim3(C / 128, R / 128), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(x), R, C, row_map, map_mode, k, static_cast<uint8_t*>(q), s,
-        static_cast<uint8_t*>(e8), static_cast<uint8_t*>(sf_atoms));
-    DK_CUDA_OK(cudaGetLastError());
-    return DK_OK;
+    DK_REQUIRE(R == 0 || sf_atoms != nullptr, "null buffer");
+    return quant_block128_launch(x, R, C, row_map, map_mode, k, nullptr, nullptr, q, s, e8, sf_atoms, true,
+                                 EpWait{}, static_cast<cudaStream_t>(stream));
 }
 
 int dk_moe_combine(const void* y, const int* row_of_pair, const float* topk_w, int T, int k, int H,

@@ -64,19 +64,30 @@ struct DispatchArgs {
     const int* topk_idx;   // [T_loc, k]
     const int* row_of_pair;  // [T_loc, k] row inside the destination rank's receive buffer
     uint4* recv[DK_MAX_RANKS];  // receive buffer of rank r as seen from here, [rows, H/8]
-    int T_loc, k, hvec, experts_per_rank;
+    int T_loc, k, hvec, experts_per_rank, world;
+    unsigned* status;
 };
+enum : unsigned { SITE_EP_DEST = 82 };
 __global__ void __launch_bounds__(256) moe_dispatch_kernel(const DispatchArgs a) {
     const int t = blockIdx.x;
     __shared__ int dst_s[8], row_s[8];
     if (threadIdx.x < a.k) {
-        dst_s[threadIdx.x] = a.topk_idx[static_cast<size_t>(t) * a.k + threadIdx.x] / a.experts_per_rank;
-        row_s[threadIdx.x] = a.row_of_pair[static_cast<size_t>(t) * a.k + threadIdx.x];
+        const int e = a.topk_idx[static_cast<size_t>(t) * a.k + threadIdx.x];
+        int d = e >= 0 ? e / a.experts_per_rank : -1;
+        int row = a.row_of_pair[static_cast<size_t>(t) * a.k + threadIdx.x];
+        if (d < 0 || d >= a.world) {  // an expert no rank of this job holds: the pair is not sent
+            record_bad_index(a.status, SITE_EP_DEST, static_cast<unsigned>(t * a.k + threadIdx.x));
+            row = -1;
+            d = 0;
+        }
+        dst_s[threadIdx.x] = d;
+        row_s[threadIdx.x] = row;
     }
     __syncthreads();
     for (int c = threadIdx.x; c < a.hvec; c += blockDim.x) {
         const uint4 v = a.x[static_cast<size_t>(t) * a.hvec + c];
-        for (int j = 0; j < a.k; ++j) a.recv[dst_s[j]][static_cast<size_t>(row_s[j]) * a.hvec + c] = v;
+        for (int j = 0; j < a.k; ++j)
+            if (row_s[j] >= 0) a.recv[dst_s[j]][static_cast<size_t>(row_s[j]) * a.hvec + c] = v;
     }
 }
 
@@ -86,15 +97,24 @@ struct CombineEpArgs {
     const int* row_of_pair;
     const float* w;
     uint4* out;  // [T_loc, H/8]
-    int T_loc, k, hvec, experts_per_rank;
+    int T_loc, k, hvec, experts_per_rank, world;
+    unsigned* status;
 };
 __global__ void __launch_bounds__(256) moe_combine_ep_kernel(const CombineEpArgs a) {
     const int t = blockIdx.x;
     __shared__ int dst_s[8], row_s[8];
     __shared__ float w_s[8];
     if (threadIdx.x < a.k) {
-        dst_s[threadIdx.x] = a.topk_idx[static_cast<size_t>(t) * a.k + threadIdx.x] / a.experts_per_rank;
-        row_s[threadIdx.x] = a.row_of_pair[static_cast<size_t>(t) * a.k + threadIdx.x];
+        const int e = a.topk_idx[static_cast<size_t>(t) * a.k + threadIdx.x];
+        int d = e >= 0 ? e / a.experts_per_rank : -1;
+        int row = a.row_of_pair[static_cast<size_t>(t) * a.k + threadIdx.x];
+        if (d < 0 || d >= a.world) {
+            record_bad_index(a.status, SITE_EP_DEST, static_cast<unsigned>(t * a.k + threadIdx.x));
+            row = -1;
+            d = 0;
+        }
+        dst_s[threadIdx.x] = d;
+        row_s[threadIdx.x] = row;
         w_s[threadIdx.x] = a.w[static_cast<size_t>(t) * a.k + threadIdx.x];
     }
     __syncthreads();
@@ -103,7 +123,8 @@ __global__ void __launch_bounds__(256) moe_combine_ep_kernel(const CombineEpArgs
         uint4 v[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-            if (j < a.k) v[j] = __ldcg(a.y[dst_s[j]] + static_cast<size_t>(row_s[j]) * a.hvec + c);
+            if (j < a.k) v[j] = row_s[j] >= 0 ? __ldcg(a.y[dst_s[j]] + static_cast<size_t>(row_s[j]) * a.hvec + c)
+                                              : make_uint4(0, 0, 0, 0);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             if (j < a.k) {
@@ -215,6 +236,9 @@ int dk_moe_dispatch(const void* x, const int* topk_idx, const int* row_of_pair, 
         a.k = k;
         a.hvec = H / 8;
         a.experts_per_rank = experts_per_rank;
+        a.world = view->world;
+        rc = device_status_ptr(&a.status);
+        if (rc != DK_OK) return rc;
         for (int r = 0; r < view->world; ++r)
             a.recv[r] = static_cast<uint4*>(view->world > 1 ? peer_ptr(view, xrecv, r) : xrecv);
         moe_dispatch_kernel<<<T_loc, 256, 0, st>>>(a);
@@ -251,6 +275,9 @@ int dk_moe_combine_ep(const void* y, const int* topk_idx, const int* row_of_pair
         a.k = k;
         a.hvec = H / 8;
         a.experts_per_rank = experts_per_rank;
+        a.world = view->world;
+        rc = device_status_ptr(&a.status);
+        if (rc != DK_OK) return rc;
         for (int r = 0; r < view->world; ++r)
             a.y[r] = static_cast<const uint4*>(view->world > 1 ? peer_ptr(view, y, r) : y);
         moe_combine_ep_kernel<<<T_loc, 256, 0, st>>>(a);

@@ -52,6 +52,7 @@ struct GroupedArgs {
     const float* xs;     // [R/128, K/128]
     const float* ws;     // [E, w_blocks, K/128]
     int E, K, N;         // N: output columns (gated: F)
+    int R;               // rows of X and of the output
     int num_kb;          // K / 128
     int n_tiles;         // gated: F/128, plain: N/256
     int w_rows;          // rows of one expert's weight: gated 2F, plain N
@@ -63,7 +64,7 @@ struct GroupedArgs {
     long long* dbg;  // [gridDim.x][DBG_SLOTS] stall counters, or null
 };
 
-enum : unsigned { GS_EMPTY = 32, GS_FULL = 33, GS_TEMPTY = 34, GS_TFULL = 35, GS_EPI = 36 };
+enum : unsigned { GS_EMPTY = 32, GS_FULL = 33, GS_TEMPTY = 34, GS_TFULL = 35, GS_EPI = 36, GS_OFFSETS = 37 };
 
 // Tile walk shared by all roles: tile t -> (expert, row0, n). cum[e] = tiles before expert e.
 struct TileWalk {
@@ -148,12 +149,16 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
     }
     __syncthreads();
     if (threadIdx.x == 0) {
+        // The offsets come from device memory: an expert whose row range is not made of whole
+        // 128-row tiles inside the output gets no tiles (and is recorded), so that no role ever
+        // forms an address from it.
         int run = 0;
         for (int e = 0; e < g.E; ++e) {
             cum_sm[e] = run;
-            int rows = offs_sm[e + 1] - offs_sm[e];
-            if (rows < 0) rows = 0;
-            run += (rows / GM) * g.n_tiles;
+            const int lo = offs_sm[e], hi = offs_sm[e + 1];
+            const bool ok = lo >= 0 && hi >= lo && hi <= g.R && (lo % GM) == 0 && (hi % GM) == 0;
+            if (ok) run += ((hi - lo) / GM) * g.n_tiles;
+            else if (blockIdx.x == 0) record_bad_index(g.status, GS_OFFSETS, static_cast<unsigned>(e));
         }
         cum_sm[g.E] = run;
     }
@@ -424,6 +429,7 @@ extern "C" int dk_moe_grouped_gemm_fp8(const void* xq, const float* xs, const vo
     g.E = E;
     g.K = K;
     g.N = N;
+    g.R = R;
     g.num_kb = K / GK;
     g.n_tiles = gated ? N / 128 : N / GN;
     g.w_rows = w_rows;

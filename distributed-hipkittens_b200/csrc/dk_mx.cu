@@ -163,12 +163,7 @@ mx_gemm_kernel(const __grid_constant__ MxMaps maps, const MxArgs g) {
             const int lo = offs_sm[e], hi = offs_sm[e + 1];
             const bool ok = lo >= 0 && hi >= lo && hi <= g.rows_pad && (lo % XM) == 0 && (hi % XM) == 0;
             if (ok) run += ((hi - lo) / XM) * g.n_tiles;
-            else if (blockIdx.x == 0 && g.status != nullptr && atomicCAS(g.status, 0u, DK_DEV_BAD_INDEX) == 0u) {
-                g.status[1] = 0;
-                g.status[2] = XS_OFFSETS;
-                g.status[3] = static_cast<unsigned>(e);
-                __threadfence_system();
-            }
+            else if (blockIdx.x == 0) record_bad_index(g.status, XS_OFFSETS, static_cast<unsigned>(e));
         }
         cum_sm[g.E] = run;
     }

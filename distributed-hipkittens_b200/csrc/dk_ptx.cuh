@@ -107,6 +107,17 @@ static __device__ __noinline__ void record_timeout(const WaitCtx& w, unsigned co
     }
 }
 
+// A kernel that meets an index from device memory pointing outside its buffers skips the access and
+// leaves this record (first one wins) for the host: {DK_DEV_BAD_INDEX, block, site, detail}.
+static __device__ __noinline__ void record_bad_index(unsigned* status, unsigned site, unsigned detail) {
+    if (status != nullptr && atomicCAS(status, 0u, static_cast<unsigned>(DK_DEV_BAD_INDEX)) == 0u) {
+        status[1] = blockIdx.x;
+        status[2] = site;
+        status[3] = detail;
+        __threadfence_system();
+    }
+}
+
 // Bounded wait on an mbarrier phase. Returns false when the limit ran out or another role of
 // this CTA already gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& w,

@@ -12,10 +12,8 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
-#include <map>
 #include <stdexcept>
 #include <string>
-#include <tuple>
 #include <vector>
 
 #include "dk_b200.h"
@@ -111,10 +109,6 @@ void dispatch_micro3(py::object A, py::object Bt, py::object C) {
     throw_on(dk_gemm_bf16(a.ptr, b.ptr, c.ptr, M, N, K, nullptr, -1, current_stream()), "dispatch_micro");
 }
 
-// One reduce-scatter workspace per (heap, M, N), allocated from the heap on first use. Every rank
-// makes the same calls in the same order, so the offsets agree.
-std::map<std::tuple<uintptr_t, int, int>, void*> g_rs_workspaces;
-
 void gemm_rs(py::object A, py::object Bt, py::object Out, py::object view) {
     TensorArg a = tensor_arg(A, "torch.bfloat16");
     TensorArg b = tensor_arg(Bt, "torch.bfloat16");
@@ -129,19 +123,9 @@ void gemm_rs(py::object A, py::object Bt, py::object Out, py::object view) {
     if (o.shape[0] * world != M || o.shape[1] != N) throw std::runtime_error("Out must be [M/world, N]");
     void* ws = nullptr;
     void* stream = current_stream();
-    if (world > 1) {
-        auto key = std::make_tuple(reinterpret_cast<uintptr_t>(v->heap), M, N);
-        auto it = g_rs_workspaces.find(key);
-        if (it == g_rs_workspaces.end()) {
-            const size_t bytes = dk_gemm_rs_workspace_bytes(M, N, world);
-            ws = dk_heap_alloc(static_cast<dk_heap*>(v->heap), bytes, 1024);
-            if (ws == nullptr) throw std::runtime_error("Failed to allocate iris memory");
-            throw_on(dk_gemm_rs_workspace_init(ws, bytes, v, stream), "gemm_rs workspace");
-            g_rs_workspaces[key] = ws;
-        } else {
-            ws = it->second;
-        }
-    }
+    // the workspace for this (M, N) belongs to the heap of the view: made on first use (every rank
+    // makes the same calls in the same order, so the offsets agree), gone when the heap goes
+    throw_on(dk_gemm_rs_workspace_get(v, M, N, stream, &ws), "gemm_rs workspace");
     throw_on(dk_gemm_rs(a.ptr, b.ptr, o.ptr, M, N, Kloc, ws, v, stream), "gemm_rs");
 }
 
@@ -350,6 +334,57 @@ py::object moe_combine(py::object Y, py::object topk_idx, py::object row_of_pair
     return out;
 }
 
+// One expert-parallel MoE layer through a single call (dk_moe_ep_layer). `Workspace` is a uint8 tensor
+// of moe_ep_workspace_bytes(...) bytes; with more than one rank it must come from the symmetric heap
+// (iris.empty([bytes], "uint8")), allocated at the same point of every rank's program.
+int64_t moe_ep_workspace_bytes(int T_loc, int k, int E, int H, int F, int world) {
+    return static_cast<int64_t>(dk_moe_ep_workspace_bytes(T_loc, k, E, H, F, world));
+}
+
+py::object moe_layer_ep(py::object X, py::object logits, int k, py::object W13q, py::object W13s, py::object W2q,
+                        py::object W2s, py::object Out, py::object Workspace, py::object view, int scale_mode,
+                        py::object counts) {
+    TensorArg x = tensor_arg(X, "torch.bfloat16"), lg = tensor_arg(logits, "torch.float32");
+    TensorArg w13q = tensor_arg(W13q, "torch.uint8"), w2q = tensor_arg(W2q, "torch.uint8");
+    TensorArg w13s = tensor_arg(W13s, scale_mode == 1 ? "torch.uint8" : "torch.float32");
+    TensorArg w2s = tensor_arg(W2s, scale_mode == 1 ? "torch.uint8" : "torch.float32");
+    TensorArg out = tensor_arg(Out, "torch.bfloat16"), ws = tensor_arg(Workspace, "torch.uint8");
+    if (x.shape.size() != 2 || lg.shape.size() != 2 || w13q.shape.size() != 3 || w2q.shape.size() != 3)
+        throw std::runtime_error("expected X [T_loc,H], logits [T_loc,E], W13q [E/P,2F,H], W2q [E/P,H,F]");
+    const dk_view* v = view_arg(view);
+    const int world = v ? v->world : 1;
+    dk_moe_ep_args a{};
+    a.T_loc = static_cast<int>(x.shape[0]);
+    a.H = static_cast<int>(x.shape[1]);
+    a.E = static_cast<int>(lg.shape[1]);
+    a.k = k;
+    a.F = static_cast<int>(w2q.shape[2]);
+    a.scale_mode = scale_mode;
+    if (lg.shape[0] != a.T_loc || w13q.shape[0] * world != a.E || w13q.shape[1] != 2 * a.F || w13q.shape[2] != a.H ||
+        w2q.shape[0] * world != a.E || w2q.shape[1] != a.H || out.numel() != x.numel())
+        throw std::runtime_error("MoE layer shapes disagree");
+    const size_t need = dk_moe_ep_workspace_bytes(a.T_loc, a.k, a.E, a.H, a.F, world);
+    if (need == 0) throw std::runtime_error("unsupported MoE layer shape");
+    if (static_cast<size_t>(ws.numel()) < need)
+        throw std::runtime_error("workspace too small: " + std::to_string(ws.numel()) + " < " + std::to_string(need));
+    a.x = x.ptr;
+    a.logits = static_cast<const float*>(lg.ptr);
+    a.w13q = w13q.ptr;
+    a.w13s = w13s.ptr;
+    a.w2q = w2q.ptr;
+    a.w2s = w2s.ptr;
+    a.out = out.ptr;
+    a.workspace = ws.ptr;
+    a.counts_out = nullptr;
+    if (!counts.is_none()) {
+        TensorArg c = tensor_arg(counts, "torch.int32");
+        if (c.numel() * world != a.E) throw std::runtime_error("counts must hold E / world entries");
+        a.counts_out = static_cast<int*>(c.ptr);
+    }
+    throw_on(dk_moe_ep_layer(&a, v, 0, 15, current_stream()), "moe_layer_ep");
+    return Out;
+}
+
 py::tuple device_status() {
     unsigned st[4] = {0, 0, 0, 0};
     throw_on(dk_last_device_status(st), "device_status");
@@ -387,6 +422,13 @@ PYBIND11_MODULE(tk_kernel, m) {
           "(power-of-two block scales applied by the tensor core)");
     m.def("moe_dispatch", &moe_dispatch, "push local tokens into the destination ranks' receive rows");
     m.def("moe_combine", &moe_combine, "Out[T_loc,H] = sum_j w_j * Y_dest[row_j]; pulls from peers when world > 1");
+    m.def("moe_ep_workspace_bytes", &moe_ep_workspace_bytes, "bytes of workspace moe_layer_ep needs");
+    m.def("moe_layer_ep", &moe_layer_ep, py::arg("X"), py::arg("logits"), py::arg("k"), py::arg("W13q"),
+          py::arg("W13s"), py::arg("W2q"), py::arg("W2s"), py::arg("Out"), py::arg("Workspace"), py::arg("view"),
+          py::arg("scale_mode") = 0, py::arg("counts") = py::none(),
+          "One fp8 MoE layer, expert-parallel over the ranks of the view, in one call: route, exchange, "
+          "dispatch (once per token and GPU), quantise, gate/up + SiLU*mul, down, combine. "
+          "scale_mode 0: fp32 block scales; 1: power-of-two block scales on the block-scaled MMA");
     m.def("device_status", &device_status,
           "(code, block, site, detail) of the first device-side wait that gave up; clears it");
 }

@@ -156,6 +156,12 @@ int dk_gemm_bf16(const void* A, const void* Bt, void* C, int M, int N, int K,
  */
 size_t dk_gemm_rs_workspace_bytes(int M, int N, int world);
 int dk_gemm_rs_workspace_init(void* workspace, size_t bytes, const dk_view* view, void* stream);
+/*
+ * The heap's own workspace for an (M, N) reduce-scatter: allocated from the heap and initialised on
+ * first use (a collective: every rank makes the same calls in the same order), then returned again
+ * for the same (M, N). It belongs to the heap and goes away with it. *out is NULL for world == 1.
+ */
+int dk_gemm_rs_workspace_get(const dk_view* view, int M, int N, void* stream, void** out);
 int dk_gemm_rs(const void* A, const void* Bt, void* out, int M, int N, int Kloc, void* workspace,
                const dk_view* view, void* stream);
 /*
@@ -370,6 +376,54 @@ int dk_moe_dispatch(const void* x, const int* topk_idx, const int* row_of_pair, 
 int dk_moe_combine_ep(const void* y, const int* topk_idx, const int* row_of_pair, const float* topk_w,
                       int T_loc, int k, int H, int experts_per_rank, void* out, const dk_view* view,
                       int sync, void* stream);
+
+/*
+ * dk_moe_ep_layer: one fp8 MoE layer, expert-parallel over the ranks of the view, as ONE host call
+ * that allocates nothing: routing, exchange of the routing table, permutation, dispatch, block
+ * quantisation, gate/up + SiLU*mul + requantise, down, combine. No counterpart in the reference.
+ *
+ *  - Token t lives on rank t / T_loc, expert e on rank e / (E / world).
+ *  - Dispatch sends each token ONCE to every rank that holds at least one of its experts (not once
+ *    per expert); the receiving rank replicates it into its experts' rows while quantising.
+ *  - Combine happens on the expert side: per (token, rank) one fp32 weighted sum of that rank's
+ *    expert outputs, pushed back as one bf16 vector; the home rank adds the partials in rank order.
+ *  - Work is bounded by the rows that actually arrived (the experts' offsets are read on the device).
+ *  - No barrier launches: producers publish a per-source flag when their last CTA is done, consumers
+ *    wait (bounded, see dk_set_peer_wait_ms) for all sources before they read.
+ *
+ * scale_mode 0: 128x128 blocks with fp32 scales (w13s [E/P, 2F/128, H/128], w2s [E/P, H/128, F/128]
+ * fp32; dk_moe_grouped_gemm_fp8). scale_mode 1: the same blocks with power-of-two scales applied by
+ * the tensor core (w13s, w2s are block atoms as dk_quant_block128_pow2 writes them;
+ * dk_moe_grouped_gemm_mxfp8). H % 256 == 0, F % 128 == 0, E <= 256, k <= 8.
+ *
+ * workspace: dk_moe_ep_workspace_bytes(...) bytes, 256-byte aligned; for world > 1 inside the
+ * symmetric heap at the same offset on every rank. Its contents need no initialisation. Calls on
+ * one workspace must not overlap on the GPU. counts_out (device, may be NULL) receives the number of
+ * pairs routed to each of this rank's E / world experts.
+ *
+ * `epoch`: 0 takes the next epoch of the view's heap (every rank calls in the same order); views
+ * without a heap handle pass the 1-based call number. `phases` selects what is enqueued: 1 routing +
+ * exchange, 2 permutation + dispatch, 4 experts + combine push, 8 final sum; 15 = the layer. Running
+ * all ranks of a job on one GPU means phase by phase over the ranks (no launch then waits for a
+ * later one).
+ */
+typedef struct dk_moe_ep_args {
+    int T_loc, k, E, H, F;
+    int scale_mode;
+    const void* x;        /* [T_loc, H] bf16 */
+    const float* logits;  /* [T_loc, E] fp32 */
+    const void* w13q;     /* [E/P, 2F, H] e4m3: gate rows, then up rows */
+    const void* w13s;
+    const void* w2q;      /* [E/P, H, F] e4m3 */
+    const void* w2s;
+    void* out;            /* [T_loc, H] bf16 */
+    void* workspace;
+    int* counts_out;
+    void* ev_gemm_begin;  /* optional cudaEvent_t handles recorded on the stream just before and just */
+    void* ev_gemm_end;    /* after the two grouped GEMMs (for timing them inside the layer); NULL: none */
+} dk_moe_ep_args;
+size_t dk_moe_ep_workspace_bytes(int T_loc, int k, int E, int H, int F, int world);
+int dk_moe_ep_layer(const dk_moe_ep_args* args, const dk_view* view, unsigned epoch, int phases, void* stream);
 
 /* ------------------------------------------------------------------ device helpers */
 /* For hosts that link this library but not the CUDA runtime (the pybind11 modules). */
