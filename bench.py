@@ -8,9 +8,9 @@ One process per GPU (under torchrun for N > 1). The default workload, the one th
 is quoted on, is the row-parallel bf16 GEMM fused with reduce-scatter: tokens M=8192, K=28672 split
 K/N across the N ranks, N=8192 outputs (the Llama-70B MLP down-projection shape), output
 reduce-scattered along M. Total work is fixed as N grows (strong scaling); at N=1 the operator is
-the plain GEMM. The other workloads measure the remaining operators of the path on the shapes
-BASELINE.json names (TP all-reduce of 1 MiB / 128 MiB; Mixtral- and DeepSeek-V3-shaped fp8 MoE
-layers, expert-parallel when N > 1).
+the plain GEMM. The other workloads measure the remaining operators of the path (TP all-reduce of
+1 MiB / 128 MiB; Mixtral- and DeepSeek-V3-shaped fp8 MoE layers, expert-parallel when N > 1); the
+default run appends them to the same JSON line as `secondary`.
 
 Prints ONE JSON line (rank 0). `value` is whole-job throughput with inputs resident in HBM, timed
 with CUDA events, max over ranks. `e2e` is the same metric through the Python entry points with
@@ -36,7 +36,7 @@ sys.path.insert(0, str(ROOT / "distributed-hipkittens_b200"))
 
 M_TOK, K_FULL, N_OUT = 8192, 28672, 8192
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-NVLINK_GBS = 770.0   # measured peer copy per direction on this pool (nominal 900)
+NVLINK_GBS = 770.0   # measured peer copy per direction over NVLink 5 / NVSwitch (nominal 900)
 
 
 def load_peaks():
@@ -409,7 +409,7 @@ class AllReduce:
         ach = self.work / (ms_step * 1e-3) / 1e9
         return {"bound": "nvlink", "achieved": ach, "peak": NVLINK_GBS, "unit": "GB/s",
                 "frac": ach / NVLINK_GBS, "traffic": None,
-                "peak_source": "measured peer copy per direction on this pool (770 GB/s)"}
+                "peak_source": "measured peer copy per direction, 770 GB/s (nominal 900)"}
 
 
 class Moe:

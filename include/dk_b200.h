@@ -147,7 +147,7 @@ int dk_gemm_bf16(const void* A, const void* Bt, void* C, int M, int N, int K,
  * staging slot over NVLink and summed there in fp32 in rank order. M % (world*128) == 0.
  * The reference has no reduce-scatter (its kernel stores to its own rank only,
  * distributed-kernels/bf16_gemm/kernel.cpp:39,58-59; `row_offset` is accepted and unused, :80);
- * this is the operation BASELINE's configs name, behind the same calling convention.
+ * this is the tensor-parallel down-projection (GEMM + reduce-scatter), behind the same calling convention.
  *
  * `workspace` is dk_gemm_rs_workspace_bytes(M, N, world) bytes allocated from the symmetric heap
  * at the same offset on every rank and initialised once, collectively, with

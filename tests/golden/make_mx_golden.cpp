@@ -7,8 +7,9 @@
 // block e8m0 = clamp(floor(log2(amax)) + 127, 0, 254) (0 for an all-zero block),
 // q = e4m3(x * 2^(127 - e8m0)); expectation c[i][j] = sum over blocks of
 // (a_q * 2^(sa-127)) * (b_q * 2^(sb-127)) accumulated in fp32 in k order.
-// This file restates that procedure (it contains none of the reference's code); the float -> e4m3
-// conversion is this repository's own (round to nearest even, saturating at 448).
+// This file restates that procedure step by step (test infrastructure; the e8m0 rule is the
+// fixture's own formula); the float -> e4m3 conversion is this repository's own (round to nearest
+// even, saturating at 448).
 //
 // Output (binary, little endian) on stdout: the first ROWS rows of A and of B as fp32, their e4m3
 // bytes and e8m0 scales, and c_ref [ROWS, ROWS]. make_golden.py turns it into mx_fixture.npz.

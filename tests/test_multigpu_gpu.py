@@ -93,10 +93,66 @@ def _worker(rank, world, job, q):
             moe_errs.append(orc.rel_fro(out_moe.float().cpu(), want_moe))
         res["moe_ep"] = moe_errs
         res["moe_idx_ok"] = bool(torch.equal(all_idx.cpu(), idx_c))
+
+        # ---- the same layer as ONE call (dedup dispatch, expert-side combine, flags instead of
+        # barriers), fp32 scales then power-of-two scales, two calls each on one workspace
+        nbytes = tk_kernel.moe_ep_workspace_bytes(Tl, k, E, H, F, world)
+        ws = torch.as_tensor(iris.empty([nbytes], "uint8"), device="cuda")
+        ws.fill_(0xFF)                       # its contents need no initialisation
+        counts = torch.empty(epr, dtype=torch.int32, device="cuda")
+        out_l = torch.empty(Tl, H, dtype=torch.bfloat16, device="cuda")
+        layer_errs = []
+        torch.cuda.synchronize()
+        iris.barrier()
+        for scale_mode in (0, 1):
+            if scale_mode == 0:
+                a13, a2 = w13s[es].contiguous().cuda(), w2s[es].contiguous().cuda()
+                q13, q2 = w13q[es].contiguous().cuda(), w2q[es].contiguous().cuda()
+                want_l = want_moe
+            else:
+                import math
+                g = torch.Generator().manual_seed(99)
+                p13 = [orc.quant_block128_pow2((torch.randn(2 * F, H, generator=g) / math.sqrt(H)).to(torch.bfloat16))
+                       for _ in range(E)]
+                p2 = [orc.quant_block128_pow2((torch.randn(H, F, generator=g) / math.sqrt(F)).to(torch.bfloat16))
+                      for _ in range(E)]
+                st = lambda parts, i: torch.stack([t[i] for t in parts])
+                xq_p, xs_p, _ = orc.quant_block128_pow2(orc.moe_gather_rows(x, por_c, k))
+                y_p = orc.moe_ffn_pow2_ref(xq_p, xs_p, st(p13, 0), st(p13, 1), st(p2, 0), st(p2, 1), offs_c)[0]
+                want_l = orc.moe_combine_ref(y_p, rop_c, w_c)[sl]
+                q13, q2 = st(p13, 0)[es].contiguous().cuda(), st(p2, 0)[es].contiguous().cuda()
+                e13, e2 = st(p13, 2)[es], st(p2, 2)[es]
+                a13 = orc.block128_scales_to_block_atoms(e13.reshape(-1, e13.shape[-1])).cuda()
+                a2 = orc.block128_scales_to_block_atoms(e2.reshape(-1, e2.shape[-1])).cuda()
+            for _ in range(2):
+                out_l.fill_(float("nan"))
+                tk_kernel.moe_layer_ep(x[sl].contiguous().cuda(), logits[sl].contiguous().cuda(), k, q13, a13, q2, a2,
+                                       out_l, ws, view, scale_mode, counts)
+                torch.cuda.synchronize()
+                layer_errs.append(orc.rel_fro(out_l.float().cpu(), want_l))
+        res["moe_layer"] = layer_errs
+        want_counts = torch.bincount(idx_c.reshape(-1).long(), minlength=E)[es]
+        res["moe_layer_counts_ok"] = bool(torch.equal(counts.cpu().long(), want_counts))
+        iris.barrier()
+        del ws
         res["status"] = tk_kernel.device_status()
         iris.barrier()
-        q.put((rank, res))
         del out, x, o, view, all_idx, xrecv, ybuf
+        del iris
+        # ---- a second heap in the same process: its reduce-scatter workspace is its own (the first
+        # heap's workspaces went away with it)
+        iris = iris_py.Iris(heap_size_mb=192)
+        view = iris.get_device_view()
+        out = torch.as_tensor(iris.empty([M // world, N]), device="cuda").view(torch.bfloat16)
+        out.fill_(float("nan"))
+        iris.barrier()
+        tk_kernel.gemm_rs(dA, dB, out, view)
+        torch.cuda.synchronize()
+        res["gemm_rs_second_heap"] = orc.rel_fro(out.float().cpu(), want)
+        res["status2"] = tk_kernel.device_status()
+        iris.barrier()
+        q.put((rank, res))
+        del out, view
         del iris
     except Exception as e:  # report instead of hanging the parent
         import traceback
@@ -123,6 +179,9 @@ def test_peer_memory_path(world):
         assert all(e <= 1e-2 for e in results[r]["gemm_rs"]), results[r]["gemm_rs"]
         assert results[r]["moe_idx_ok"]
         assert all(e <= 2e-2 for e in results[r]["moe_ep"]), results[r]["moe_ep"]
+        assert all(e <= 2e-2 for e in results[r]["moe_layer"]), results[r]["moe_layer"]
+        assert results[r]["moe_layer_counts_ok"]
+        assert results[r]["gemm_rs_second_heap"] <= 1e-2 and results[r]["status2"][0] == 0
         for algo in (0, 1, -1):
             assert results[r][f"allreduce{algo}"] <= 1e-2
             # every rank holds the same bits

@@ -36,6 +36,13 @@ def _run_static(capi, idx, E, pad, seg):
     return rop, por, offs, counts
 
 
+def _device_bytes_free():
+    """Free device memory as the driver reports it (cudaMemGetInfo): it moves when anything on the
+    device is allocated or released behind torch's caching allocator."""
+    torch.cuda.synchronize()
+    return torch.cuda.mem_get_info()[0]
+
+
 def test_static_permute_matches_allocating_entry_point_twice(capi, orc):
     assert capi.lib().dk_moe_permute_static_max_bytes() == 256 * 1024
     g = torch.Generator().manual_seed(123)
@@ -48,6 +55,36 @@ def test_static_permute_matches_allocating_entry_point_twice(capi, orc):
         torch.cuda.synchronize()
         for a, b in zip(got, want):
             assert torch.equal(a.reshape(-1), b.reshape(-1))
+
+
+def test_static_permute_leaves_device_memory_as_it_found_it(capi, orc):
+    """The property the entry point exists for: with the outputs already there, a call (after the
+    first one on the device, which looks the scratch array up) changes the amount of device memory
+    in use by nothing, as the driver counts it."""
+    L = capi.lib()
+    T, E, k, seg, pad = 4096, 64, 4, 64, 128
+    idx, _ = orc.moe_route(torch.randn(T, E, generator=torch.Generator().manual_seed(7)), k)
+    d_idx = idx.cuda()
+    cap = L.dk_moe_rows_capacity(T, k, seg, pad)
+    rop = torch.empty((T, k), dtype=torch.int32, device="cuda")
+    por = torch.empty((1, cap), dtype=torch.int32, device="cuda")
+    offs = torch.empty((1, seg + 1), dtype=torch.int32, device="cuda")
+    counts = torch.empty((E,), dtype=torch.int32, device="cuda")
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    P = lambda t: C.c_void_p(t.data_ptr())
+
+    def call():
+        capi.check(L.dk_moe_permute_static(P(d_idx), T, k, E, pad, seg, P(rop), P(por), cap, P(offs), P(counts),
+                                           stream))
+    call()                                  # first call on this device: set-up happens here
+    before = _device_bytes_free()
+    for _ in range(3):
+        call()
+    after = _device_bytes_free()
+    assert after == before, (before, after)
+    want = capi.moe_permute(d_idx, E, pad, experts_per_segment=seg)
+    for a, b in zip((rop, por, offs, counts), want):
+        assert torch.equal(a.reshape(-1), b.reshape(-1))
 
 
 def test_static_permute_rejects_oversized_routing(capi):
