@@ -135,10 +135,18 @@ __global__ void __launch_bounds__(ROUTE_MAX_E) moe_scan_kernel(int* __restrict__
     const int e = threadIdx.x;
     if (e < E) {
         int run = 0;
-        for (int c = 0; c < nchunks; ++c) {  // exclusive scan over chunks, in place
-            const int v = chunk_counts[static_cast<size_t>(c) * E + e];
-            chunk_counts[static_cast<size_t>(c) * E + e] = run;
-            run += v;
+        // exclusive scan over chunks, in place; eight independent loads at a time (the loop is bound
+        // by load latency, not by the additions)
+        for (int c0 = 0; c0 < nchunks; c0 += 8) {
+            int v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                v[i] = c0 + i < nchunks ? chunk_counts[static_cast<size_t>(c0 + i) * E + e] : 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (c0 + i < nchunks) chunk_counts[static_cast<size_t>(c0 + i) * E + e] = run;
+                run += v[i];
+            }
         }
         counts[e] = run;
         padded[e] = (run + pad - 1) / pad * pad;
@@ -213,7 +221,7 @@ __global__ void __launch_bounds__(PERM_CHUNK) moe_place_kernel(const int* __rest
 // block-scaled tensor-core path reads: per 128 rows and four column blocks one 512-byte atom whose
 // byte r*4 + g (r = row slot 0..127, g = 0..3) is the byte of column block 4j + g.
 template <bool POW2>
-__global__ void __launch_bounds__(256) quant_block128_kernel(const __nv_bfloat16* __restrict__ x, int R, int C,
+__global__ void __launch_bounds__(256, 4) quant_block128_kernel(const __nv_bfloat16* __restrict__ x, int R, int C,
                                                              const int* __restrict__ map, int map_mode,
                                                              int k, uint8_t* __restrict__ q,
                                                              float* __restrict__ s, uint8_t* __restrict__ e8,
@@ -226,34 +234,38 @@ __global__ void __launch_bounds__(256) quant_block128_kernel(const __nv_bfloat16
     if (!ep_wait_sources(wait)) return;
     const int cchunk = (threadIdx.x & 15) * 8;
     const int r0 = threadIdx.x >> 4;
-    float vals[8][8];
-    float amax = 0.f;
+    // The 8 x 8 values of this thread stay packed as bf16 (32 registers instead of 64): the kernel is
+    // bound by how many row loads an SM keeps in flight, i.e. by how many CTAs fit.
+    uint4 u[8];
+    long src[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int r = br * 128 + r0 + 16 * i;
-        long src = r;
-        bool valid = true;
+        src[i] = r;
         if (map_mode != 0) {
             const int mv = map[r];
-            valid = mv >= 0;
-            if (map_mode == 1) src = valid ? mv / k : 0;
+            bool valid = mv >= 0;
+            if (map_mode == 1) src[i] = valid ? mv / k : -1;
+            if (map_mode == 2) src[i] = valid ? r : -1;
             if (map_mode == 3) {
                 const int slot = valid ? map2[mv / k] : -1;
-                valid = slot >= 0;
-                src = valid ? slot : 0;
+                src[i] = slot;
             }
         }
-        uint4 u = make_uint4(0, 0, 0, 0);
-        if (valid) u = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(src) * C + bc * 128 + cchunk);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float2 f = __bfloat1622float2(h[j]);
-            vals[i][2 * j] = f.x;
-            vals[i][2 * j + 1] = f.y;
-            amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
-        }
     }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        u[i] = make_uint4(0, 0, 0, 0);
+        if (src[i] >= 0) u[i] = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(src[i]) * C + bc * 128 + cchunk);
+    }
+    __nv_bfloat162 m2 = __float2bfloat162_rn(0.f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u[i]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) m2 = __hmax2(m2, __habs2(h[j]));  // exact: a maximum of magnitudes
+    }
+    float amax = fmaxf(__low2float(m2), __high2float(m2));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
@@ -281,18 +293,27 @@ __global__ void __launch_bounds__(256) quant_block128_kernel(const __nv_bfloat16
         if (threadIdx.x == 0 && e8 != nullptr) e8[blk] = static_cast<uint8_t>(b8);
     }
     if (threadIdx.x == 0 && s != nullptr) s[blk] = scale;
+    const float inv = 1.0f / scale;  // exact for a power of two
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int r = br * 128 + r0 + 16 * i;
-        uint8_t b[8];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u[i]);
+        uint32_t w[2];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            float y = vals[i][j] / scale;  // IEEE division: same bits as the CPU definition
-            y = fminf(fmaxf(y, -448.0f), 448.0f);
-            b[j] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3));
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            float2 y;
+            if (POW2) {
+                y = make_float2(f.x * inv, f.y * inv);
+            } else {
+                y = make_float2(f.x / scale, f.y / scale);  // IEEE division: same bits as the CPU definition
+            }
+            // |x| <= amax, so |y| <= 448 up to rounding: the saturating conversion is the clamp
+            const uint32_t p = __nv_cvt_float2_to_fp8x2(y, __NV_SATFINITE, __NV_E4M3);
+            if (j & 1) w[j >> 1] |= p << 16;
+            else w[j >> 1] = p;
         }
-        *reinterpret_cast<uint2*>(q + static_cast<size_t>(r) * C + bc * 128 + cchunk) =
-            *reinterpret_cast<const uint2*>(b);
+        *reinterpret_cast<uint2*>(q + static_cast<size_t>(r) * C + bc * 128 + cchunk) = make_uint2(w[0], w[1]);
     }
 }
 

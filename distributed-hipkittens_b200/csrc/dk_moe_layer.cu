@@ -207,16 +207,22 @@ __global__ void __launch_bounds__(256) ep_combine_push_kernel(const EpCombineArg
         uint4* dst = a.partial[home] + static_cast<size_t>(t - home * a.T_loc) * a.hvec;
         for (int c = threadIdx.x; c < a.hvec; c += blockDim.x) {
             float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            for (int j = 0; j < a.k; ++j) {
-                if (row_s[j] < 0) continue;
-                const uint4 u = a.y[static_cast<size_t>(row_s[j]) * a.hvec + c];
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-                const float wj = w_s[j];
+            uint4 v[8];
+            // all of the token's rows on this rank are requested before the first one is used
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 f = __bfloat1622float2(h[i]);
-                    acc[2 * i] += wj * f.x;
-                    acc[2 * i + 1] += wj * f.y;
+            for (int j = 0; j < 8; ++j)
+                v[j] = (j < a.k && row_s[j] >= 0) ? a.y[static_cast<size_t>(row_s[j]) * a.hvec + c] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (j < a.k && row_s[j] >= 0) {
+                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[j]);
+                    const float wj = w_s[j];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = __bfloat1622float2(h[i]);
+                        acc[2 * i] += wj * f.x;
+                        acc[2 * i + 1] += wj * f.y;
+                    }
                 }
             }
             uint4 o;
