@@ -313,6 +313,81 @@ class GemmRs:
         return r
 
 
+class AgGemm:
+    """Column-parallel GEMM fused with the all-gather of its activations: the Llama-70B MLP
+    up-projection, tokens M=8192 row-sharded over the ranks, K=8192, N=28672 split N/P per rank."""
+    metric, unit, dtype, scaling = "ag_gemm_tflops", "TFLOP/s", "bf16", "strong"
+    launches_per_step = 1
+    M, K, N = 8192, 8192, 28672
+
+    @classmethod
+    def heap_mb(cls, P):
+        return (2 * cls.M * cls.K * 2) // (1 << 20) + 64 if P > 1 else 64
+
+    def __init__(self, ctx):
+        import torch
+        self.ctx = ctx
+        P, rank = ctx.world, ctx.rank
+        ctx.make_heap(self.heap_mb(P))
+        self.Nloc, self.shard = self.N // P, self.M // P
+        g = torch.Generator(device="cuda").manual_seed(2000 + rank)
+        set_bytes = (self.shard + self.Nloc) * self.K * 2
+        self.nsets = max(2, math.ceil(256e6 / set_bytes))
+        self.sets = []
+        for _ in range(self.nsets):
+            A = torch.randn(self.shard, self.K, device="cuda", generator=g).to(torch.bfloat16)
+            Bt = (torch.randn(self.Nloc, self.K, device="cuda", generator=g) / math.sqrt(self.K)).to(torch.bfloat16)
+            self.sets.append((A, Bt))
+        self.out = torch.empty(self.M, self.Nloc, dtype=torch.bfloat16, device="cuda")
+        self.work = 2.0 * self.M * self.N * self.K
+        self.scale = 1e12
+
+    def step(self, i):
+        A, Bt = self.sets[i % self.nsets]
+        self.ctx.tk.ag_gemm(A, Bt, self.out, self.ctx.view)
+
+    def check(self):
+        """64 rows of every source shard against torch on a NCCL all-gather of the shards."""
+        import torch
+        ctx = self.ctx
+        A, Bt = self.sets[0]
+        ctx.tk.ag_gemm(A, Bt, self.out, ctx.view)
+        torch.cuda.synchronize()
+        parts = [torch.empty(64, self.K, dtype=torch.bfloat16, device="cuda") for _ in range(ctx.world)]
+        if ctx.world > 1:
+            ctx.dist.all_gather(parts, A[:64].contiguous())
+        else:
+            parts = [A[:64]]
+        err = 0.0
+        for r, p in enumerate(parts):
+            ref = p.float() @ Bt.float().T
+            got = self.out[r * self.shard:r * self.shard + 64].float()
+            err = max(err, ((got - ref).norm() / ref.norm()).item())
+        return ctx.max_over_ranks(err)
+
+    def e2e_setup(self):
+        return None
+
+    def config(self, value):
+        P = self.ctx.world
+        return {"workload": f"ag_gemm M={self.M} K={self.K} N={self.N}: activations row-sharded over {P} GPU(s), "
+                            f"weight columns split N/{P} (Llama-70B MLP up-proj shape), all-gather fused into the GEMM",
+                "l2": f"{self.nsets} operand sets rotated", "per_gpu_tflops": value / P}
+
+    def roofline(self, ms_step, sustained, peaks, peak_src):
+        P = self.ctx.world
+        peak = peaks.get("bf16_tflops_sustained" if sustained else "bf16_tflops")
+        achieved = (self.work / P) / (ms_step * 1e-3) / 1e12
+        r = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+             "frac": achieved / peak if peak else None, "traffic": None,
+             "peak_source": f"{peak_src} ({'sustained' if sustained else 'burst'} cuBLAS bf16)"}
+        if P > 1:
+            ingress = 2.0 * self.M * self.K * (P - 1) / P
+            r["nvlink"] = {"ingress_bytes_per_step": ingress, "achieved_gbs": ingress / (ms_step * 1e-3) / 1e9,
+                           "peak_gbs": NVLINK_GBS, "floor_ms": ingress / (NVLINK_GBS * 1e9) * 1e3}
+        return r
+
+
 class AllReduce:
     """TP all-reduce of bf16 activations: decode [64 x 8192] (1 MiB) and prefill [8192 x 8192]
     (128 MiB); a step is one all-reduce of each."""
@@ -739,6 +814,18 @@ def moe_secondary(ctx, which, scales, peaks, tokens=0):
     return e
 
 
+def ag_gemm_secondary(ctx, peaks, peak_src):
+    wl = AgGemm(ctx)
+    ms, _ = time_steps(ctx, wl, steps=20, warmup=5)
+    err = wl.check()
+    value = wl.work / (ms * 1e-3) / 1e12
+    e = {"workload": wl.config(value)["workload"], "step_ms": ms, "tflops_whole_job": value,
+         "tflops_per_gpu": value / ctx.world, "check_rel_fro": err, "roofline": wl.roofline(ms, False, peaks, peak_src)}
+    assert err <= 1e-2, f"all-gather + GEMM differs from the NCCL-gathered reference by {err}"
+    del wl
+    return e
+
+
 def allreduce_secondary(ctx):
     wl = AllReduce(ctx)
     ms, _ = time_steps(ctx, wl, steps=10, warmup=3)
@@ -765,7 +852,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gemm_rs",
-                    choices=["gemm_rs", "allreduce", "moe_mixtral", "moe_dsv3"])
+                    choices=["gemm_rs", "ag_gemm", "allreduce", "moe_mixtral", "moe_dsv3"])
     ap.add_argument("--scales", default="fp32", choices=["fp32", "pow2"],
                     help="MoE workloads: fp32 128x128 block scales (software promotion) or power-of-two "
                          "block scales applied by the block-scaled MMA")
@@ -805,7 +892,7 @@ def main():
     ctx = Ctx(rank, world, local_rank)
     secondary_on = args.workload == "gemm_rs" and not args.no_secondary and not args.shape
     # one symmetric heap for everything this run will do
-    need = {"gemm_rs": GemmRs.heap_mb(world), "allreduce": AllReduce.HEAP_MB}
+    need = {"gemm_rs": GemmRs.heap_mb(world), "ag_gemm": AgGemm.heap_mb(world), "allreduce": AllReduce.HEAP_MB}
     for wname in ("moe_mixtral", "moe_dsv3"):
         need[wname] = Moe.heap_mb(ctx, wname, args.tokens if args.workload == wname else 0)
     heap_mb = need[args.workload] + (sum(v for k_, v in need.items() if k_ != args.workload) if secondary_on else 0)
@@ -813,6 +900,8 @@ def main():
 
     if args.workload == "gemm_rs":
         wl = GemmRs(ctx)
+    elif args.workload == "ag_gemm":
+        wl = AgGemm(ctx)
     elif args.workload == "allreduce":
         wl = AllReduce(ctx)
     else:
@@ -928,6 +1017,7 @@ def main():
         gc.collect()
         torch.cuda.empty_cache()
         sec = {}
+        sec["ag_gemm"] = ag_gemm_secondary(ctx, peaks, peak_src)
         if world > 1:
             sec["allreduce"] = allreduce_secondary(ctx)
         for which in ("moe_mixtral", "moe_dsv3"):

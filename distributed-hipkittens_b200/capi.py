@@ -92,6 +92,12 @@ def _declare(L: C.CDLL) -> None:
     L.dk_gemm_rs_workspace_get.argtypes = [C.POINTER(DkView), i, i, vp, C.POINTER(vp)]
     L.dk_gemm_rs.argtypes = [vp, vp, vp, i, i, i, vp, C.POINTER(DkView), vp]
     L.dk_gemm_rs_phase.argtypes = [vp, vp, vp, i, i, i, vp, C.POINTER(DkView), C.c_uint, i, i, vp]
+    L.dk_ag_gemm_workspace_bytes.restype = sz
+    L.dk_ag_gemm_workspace_bytes.argtypes = [i, i, i]
+    L.dk_ag_gemm_workspace_init.argtypes = [vp, sz, C.POINTER(DkView), vp]
+    L.dk_ag_gemm_workspace_get.argtypes = [C.POINTER(DkView), i, i, vp, C.POINTER(vp)]
+    L.dk_ag_gemm.argtypes = [vp, vp, vp, i, i, i, vp, C.POINTER(DkView), vp]
+    L.dk_ag_gemm_phase.argtypes = [vp, vp, vp, i, i, i, vp, C.POINTER(DkView), C.c_uint, i, vp]
     L.dk_allreduce.argtypes = [vp, vp, sz, i, C.POINTER(DkView), vp]
     L.dk_gemm_debug_counters.argtypes = [vp]
     L.dk_gemm_pair_mode.argtypes = [i]
@@ -288,6 +294,20 @@ def gemm_rs_phase(A, Bt, out, ws_ptr, view: DkView, seq: int, phases: int, *, ep
     check(lib().dk_gemm_rs_phase(_ptr(A), _ptr(Bt), _ptr(out), M, N, Kloc, C.c_void_p(ws_ptr),
                                  C.byref(view), seq, phases, epilogue, _stream_ptr(stream)))
     return out
+
+
+def ag_gemm_workspace_bytes(M: int, K: int, world: int) -> int:
+    return lib().dk_ag_gemm_workspace_bytes(M, K, world)
+
+
+def ag_gemm_phase(A_shard, Bt, C_out, ws_ptr, view: DkView, seq: int, phases: int, stream=None):
+    """C[M, N] = all-gather over ranks of A_shard[M/P, K] @ Bt[N, K]^T; phases 1 = push, 2 = GEMM."""
+    _need_cuda(A_shard, Bt, C_out)
+    M, N = C_out.shape
+    K = A_shard.shape[1]
+    check(lib().dk_ag_gemm_phase(_ptr(A_shard), _ptr(Bt), _ptr(C_out), M, N, K, C.c_void_p(ws_ptr), C.byref(view),
+                                 seq, phases, _stream_ptr(stream)))
+    return C_out
 
 
 def allreduce(x, out, view: DkView, algo: int = -1, stream=None):

@@ -36,6 +36,16 @@
 //   warps 6-11  reducers: for every tile of this rank's own rows that this CTA computes, wait
 //               (bounded) for the `world` flags, sum the `world` bf16 partials in fp32 in rank order
 //               and write bf16, while the MMA warp is already working on the next tile.
+//
+// All-gather mode (column-parallel GEMM, the projection BEFORE the row-parallel one): the rows of A
+// are sharded over the ranks (A_r [M/P, K]), every rank needs all of them against its own columns of
+// the weight. The six warps that have nothing to do in a plain GEMM push this rank's shard into the
+// peers' staging copies of A, 16 rows at a time with 16-byte peer stores, and count each piece into a
+// per-(source, 128-row tile) counter at the destination with a release add. The TMA producer starts
+// with the tiles of its own rows (read from the caller's A), then walks the other shards in the
+// order rank+1, rank+2, ...; before the first load of a tile whose rows come from a peer it waits
+// (bounded) for that tile's counter and crosses to the async proxy with a fence. No remote tile is
+// ever read over NVLink by TMA: every CTA loads from this GPU's own memory.
 #include "dk_heap.h"
 #include "dk_host.h"
 #include "dk_ptx.cuh"
@@ -70,6 +80,7 @@ constexpr int TMEM_COLS = 512;
 
 struct GemmMaps {
     CUtensorMap a;
+    CUtensorMap a_stage;  // all-gather mode: this rank's staging copy of the whole A [M, K]
     CUtensorMap b;
     CUtensorMap out[DK_MAX_RANKS];  // destination seen as [rows_per_rank, N], box 64 x 32
 };
@@ -93,7 +104,19 @@ struct GemmArgs {
     unsigned* status;
     unsigned long long peer_wait_ns;
     long long* dbg;  // [gridDim.x][DBG_SLOTS] stall counters, or null
+    // all-gather mode (ag_world > 1); `a` then holds this rank's shard only
+    int ag_world, ag_rank;
+    int ag_shard_rows;                   // M / ag_world
+    int ag_push;                         // this launch pushes the shard to the peers
+    const uint4* ag_src;                 // this rank's shard [shard_rows, K]
+    uint4* ag_dst[DK_MAX_RANKS];         // staging copy of A at rank d (current parity), [M, K]
+    unsigned* ag_cnt_dst[DK_MAX_RANKS];  // counters [ag_world][tiles per shard] at rank d
+    const unsigned* ag_cnt;              // the local ones
+    unsigned ag_target;                  // value a counter has reached when its tile is complete
 };
+
+constexpr int AG_ROWS = 16;                  // rows per pushed piece
+constexpr int AG_PIECES = BM / AG_ROWS;      // pieces per 128-row tile
 
 enum : unsigned {
     SITE_EMPTY = 1,
@@ -101,7 +124,8 @@ enum : unsigned {
     SITE_TMEM_EMPTY = 3,
     SITE_TMEM_FULL = 4,
     SITE_EPI_DONE = 5,
-    SITE_RS_FLAG = 6
+    SITE_RS_FLAG = 6,
+    SITE_AG_TILE = 7
 };
 
 // t -> (m, n) in units of the launch's tiles (tiles_m counts tiles of 128 * PAIR rows).
@@ -295,6 +319,25 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                     int m, n;
                     tile_coords(t, g, m, n);
                     m = m * PAIR + crank;  // this CTA's 128-row tile
+                    const CUtensorMap* amap = &maps.a;
+                    int arow = m * BM;
+                    if (g.ag_world > 1) {
+                        const int src = arow / g.ag_shard_rows;
+                        if (src == g.ag_rank) {
+                            arow -= src * g.ag_shard_rows;  // own rows: straight from the caller's shard
+                        } else {
+                            // rows of a peer: wait until all pieces of this 128-row tile have landed
+                            // in the local staging copy, then make them visible to the TMA unit
+                            amap = &maps.a_stage;
+                            const int tile_in_shard = (arow - src * g.ag_shard_rows) / BM;
+                            if (!signal_wait_ge(g.ag_cnt + src * (g.ag_shard_rows / BM) + tile_in_shard, g.ag_target,
+                                                wc, SITE_AG_TILE, static_cast<unsigned>(m))) {
+                                ok = false;
+                                break;
+                            }
+                            asm volatile("fence.proxy.async;" ::: "memory");
+                        }
+                    }
                     for (int kb = 0; kb < g.num_kb; ++kb) {
                         const long long c0 = clock64();
                         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, wc, SITE_EMPTY, t)) {
@@ -310,13 +353,13 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                             // announced them (the phase cannot end before the leader's arrive)
                             const uint32_t lead_full = mapa_shared(full, 0);
                             if (crank == 0) mbar_expect_tx(full, 2 * STAGE_BYTES);
-                            tma_load_2d_pair(sa, &maps.a, lead_full, kb * BK, m * BM);
+                            tma_load_2d_pair(sa, amap, lead_full, kb * BK, arow);
                             // a pair splits the 256 rows of the Bt tile between its two CTAs
                             tma_load_2d_pair(sa + A_BYTES, &maps.b, lead_full, kb * BK,
                                              n * BN + crank * Cfg<PAIR>::B_ROWS);
                         } else {
                             mbar_expect_tx(full, STAGE_BYTES);
-                            tma_load_2d(sa, &maps.a, full, kb * BK, m * BM);
+                            tma_load_2d(sa, amap, full, kb * BK, arow);
                             tma_load_2d(sa + A_BYTES, &maps.b, full, kb * BK, n * BN);
                         }
                         if (++s == STAGES) {
@@ -503,6 +546,42 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
         }
     }
 
+    // -------------------------------------------------------- all-gather pushers (warps 6..11)
+    // Every piece is 16 rows of this rank's shard = 16 * K contiguous bf16 at the source and at the
+    // destination. Pieces are dealt round-robin to the pusher warps of the whole grid, nearest
+    // consumer first: rank d works through the shards d, d+1, ..., so the shard of rank s is needed
+    // first by s-1, then s-2, ...
+    if (warp >= 6 && g.ag_world > 1 && g.ag_push) {
+        const int tiles_shard = g.ag_shard_rows / BM;
+        const int per_peer = tiles_shard * AG_PIECES;
+        const int total = (g.ag_world - 1) * per_peer;
+        const int nvec = AG_ROWS * (g.K / 8);
+        const int nwarps = gridDim.x * 6;
+        for (int u = blockIdx.x * 6 + (warp - 6); u < total; u += nwarps) {
+            const int pi = u / per_peer;
+            int d = g.ag_rank - 1 - pi;
+            if (d < 0) d += g.ag_world;
+            const int rem = u - pi * per_peer;
+            const int rt = rem / AG_PIECES;
+            const size_t row0 = static_cast<size_t>(rt) * BM + (rem - rt * AG_PIECES) * AG_ROWS;
+            const uint4* src = g.ag_src + row0 * (g.K / 8);
+            uint4* dst = g.ag_dst[d] + (static_cast<size_t>(g.ag_rank) * g.ag_shard_rows + row0) * (g.K / 8);
+            int i = lane;
+            for (; i + 96 < nvec; i += 128) {
+                const uint4 v0 = src[i], v1 = src[i + 32], v2 = src[i + 64], v3 = src[i + 96];
+                dst[i] = v0;
+                dst[i + 32] = v1;
+                dst[i + 64] = v2;
+                dst[i + 96] = v3;
+            }
+            for (; i < nvec; i += 32) dst[i] = src[i];
+            // the lanes' stores are ordered before lane 0's release by the warp barrier; the release
+            // add is cumulative over them at system scope
+            __syncwarp();
+            if (lane == 0) signal_add_release_sys(g.ag_cnt_dst[d] + g.ag_rank * tiles_shard + rt, 1u);
+        }
+    }
+
     // -------------------------------------------------------- reducers (warps 6..11, world > 1)
     // They walk the same tile list as the GEMM roles and pick the tiles whose rows this rank owns:
     // the CTA that computes this rank's own partial of a tile (the last contribution to arrive,
@@ -647,6 +726,7 @@ int gemm_bf16_impl(const void* A, const void* Bt, void* C, int M, int N, int K, 
     rc = make_tmap_2d(&maps.out[0], C, 2, N, M, static_cast<uint64_t>(N) * 2, 64, 32);
     if (rc != DK_OK) return rc;
     for (int r = 1; r < DK_MAX_RANKS; ++r) maps.out[r] = maps.out[0];
+    maps.a_stage = maps.a;
     g.M = M;
     g.N = N;
     g.K = K;
@@ -754,6 +834,7 @@ int gemm_rs_impl(const void* A, const void* Bt, void* out, int M, int N, int Klo
     }
     // the output maps are used by the plain GEMM only; fill them with a valid descriptor
     for (int o = 0; o < DK_MAX_RANKS; ++o) maps.out[o] = maps.a;
+    maps.a_stage = maps.a;
     g.red_src = reinterpret_cast<const __nv_bfloat16*>(ws_local + stage_par);
     g.red_out = static_cast<__nv_bfloat16*>(out);
     g.red_flags = reinterpret_cast<const unsigned*>(ws_local + flags_off);
@@ -769,7 +850,171 @@ int gemm_rs_impl(const void* A, const void* Bt, void* out, int M, int N, int Klo
     return launch_gemm(maps, g, (tiles < units ? tiles : units) * pair, pair == 2, stream);
 }
 
+// ---- all-gather + GEMM -------------------------------------------------------------------------
+// Workspace layout (identical offset on every rank, inside the symmetric heap):
+//   stage [2 parities][M, K] bf16: this rank's copy of the whole A (its own rows are never written:
+//         they are read from the caller's shard), then
+//   counters [world][tiles per shard] u32 (offset rounded up to 256 bytes): pieces received so far
+//         of every 128-row tile; they only grow (AG_PIECES per call), nothing is reset.
+static size_t ag_stage_bytes(int M, int K) { return static_cast<size_t>(M) * K * 2; }
+static size_t ag_cnt_offset(int M, int K) { return (2 * ag_stage_bytes(M, K) + 255) / 256 * 256; }
+size_t ag_gemm_workspace_bytes(int M, int K, int world) {
+    if (world <= 1) return 0;
+    return ag_cnt_offset(M, K) + static_cast<size_t>(M / BM) * 4;
+}
+
+// phases: bit 0 = push this rank's shard to the peers, bit 1 = the GEMM (which waits for the peers'
+// pieces). seq = 1-based call number on this workspace.
+int ag_gemm_impl(const void* A, const void* Bt, void* C, int M, int N, int K, void* workspace, const dk_view* view,
+                 unsigned seq, int phases, cudaStream_t stream) {
+    const int world = view ? view->world : 1;
+    if (world <= 1) {
+        if ((phases & 2) == 0) return DK_OK;
+        return gemm_bf16_impl(A, Bt, C, M, N, K, -1, stream);
+    }
+    int rc = check_gemm_args(A, Bt, C, M, N, K);
+    if (rc != DK_OK) return rc;
+    DK_REQUIRE(world <= DK_MAX_RANKS, "world must be <= 8");
+    DK_REQUIRE(view->rank >= 0 && view->rank < world, "rank out of range");
+    DK_REQUIRE(M % (world * BM) == 0, "M must be a multiple of world * 128");
+    DK_REQUIRE(workspace != nullptr, "ag_gemm needs a workspace inside the symmetric heap");
+    DK_REQUIRE(seq != 0, "sequence numbers start at 1");
+    if (const int pending = device_status_pending()) return pending;
+    const int rank = view->rank;
+    const int shard = M / world;
+    GemmMaps maps;
+    GemmArgs g{};
+    const int pair = use_pair(M, shard) ? 2 : 1;
+    char* ws_local = static_cast<char*>(workspace);
+    const size_t par_off = static_cast<size_t>(seq & 1u) * ag_stage_bytes(M, K);
+    rc = make_tmap_2d(&maps.a, A, 2, K, shard, static_cast<uint64_t>(K) * 2, BK, BM);
+    if (rc != DK_OK) return rc;
+    rc = make_tmap_2d(&maps.a_stage, ws_local + par_off, 2, K, M, static_cast<uint64_t>(K) * 2, BK, BM);
+    if (rc != DK_OK) return rc;
+    rc = make_tmap_2d(&maps.b, Bt, 2, K, N, static_cast<uint64_t>(K) * 2, BK, BN / pair);
+    if (rc != DK_OK) return rc;
+    rc = make_tmap_2d(&maps.out[0], C, 2, N, M, static_cast<uint64_t>(N) * 2, 64, 32);
+    if (rc != DK_OK) return rc;
+    for (int r = 1; r < DK_MAX_RANKS; ++r) maps.out[r] = maps.out[0];
+    g.M = M;
+    g.N = N;
+    g.K = K;
+    g.tiles_m = M / BM / pair;
+    g.group_m = group_m_setting() / pair;
+    if (g.group_m < 1) g.group_m = 1;
+    g.tiles_n = (N + BN - 1) / BN;
+    g.num_kb = (K + BK - 1) / BK;
+    g.world = 1;                       // the output is local: plain epilogue, no reducers
+    g.rank = 0;
+    g.rows_per_rank = g.tiles_m * pair * BM;
+    g.tiles_per_owner = 0;
+    g.m_tile_rot = rank * (shard / BM / pair);   // own rows first, then the shards of rank+1, rank+2, ...
+    g.epi_mode = 1;
+    g.phases = (phases & 2) ? 1 : 0;
+    g.dst[0] = static_cast<__nv_bfloat16*>(C);
+    g.epoch = 0;
+    g.ag_world = world;
+    g.ag_rank = rank;
+    g.ag_shard_rows = shard;
+    g.ag_push = (phases & 1) ? 1 : 0;
+    g.ag_src = static_cast<const uint4*>(A);
+    for (int d = 0; d < world; ++d) {
+        char* ws_d = static_cast<char*>(peer_ptr(view, ws_local, d));
+        g.ag_dst[d] = reinterpret_cast<uint4*>(ws_d + par_off);
+        g.ag_cnt_dst[d] = reinterpret_cast<unsigned*>(ws_d + ag_cnt_offset(M, K));
+    }
+    g.ag_cnt = reinterpret_cast<const unsigned*>(ws_local + ag_cnt_offset(M, K));
+    g.ag_target = seq * static_cast<unsigned>(AG_PIECES);
+    rc = device_status_ptr(&g.status);
+    if (rc != DK_OK) return rc;
+    g.peer_wait_ns = peer_wait_ns();
+    g.dbg = g_gemm_dbg;
+    int sms = 0;
+    rc = sm_count(&sms);
+    if (rc != DK_OK) return rc;
+    const int tiles = g.tiles_m * g.tiles_n;
+    const int units = sms / pair;
+    // a launch that pushes uses the whole machine's pusher warps even when there are few tiles
+    const int ctas = (phases & 1) ? units : (tiles < units ? tiles : units);
+    return launch_gemm(maps, g, ctas * pair, pair == 2, stream);
+}
+
 }  // namespace dk
+
+extern "C" size_t dk_ag_gemm_workspace_bytes(int M, int K, int world) {
+    if (M <= 0 || K <= 0 || world < 1 || world > DK_MAX_RANKS || M % (world * dk::BM) != 0) return 0;
+    return dk::ag_gemm_workspace_bytes(M, K, world);
+}
+
+extern "C" int dk_ag_gemm_workspace_init(void* workspace, size_t bytes, const dk_view* view, void* stream) {
+    if (view == nullptr || view->world <= 1) return DK_OK;
+    DK_REQUIRE(workspace != nullptr && bytes > 0, "null workspace");
+    DK_REQUIRE(dk::in_heap(view, workspace, bytes), "workspace must lie inside the symmetric heap");
+    DK_CUDA_OK(cudaMemsetAsync(workspace, 0, bytes, static_cast<cudaStream_t>(stream)));
+    DK_CUDA_OK(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    dk_heap* h = static_cast<dk_heap*>(view->heap);
+    if (h != nullptr) {
+        {
+            std::lock_guard<std::mutex> lk(h->mu);
+            h->rs_seq[workspace] = 0;
+        }
+        return dk_heap_barrier(h);
+    }
+    return DK_OK;
+}
+
+extern "C" int dk_ag_gemm_phase(const void* A, const void* Bt, void* C, int M, int N, int K, void* workspace,
+                                const dk_view* view, unsigned seq, int phases, void* stream) {
+    DK_REQUIRE(phases >= 1 && phases <= 3, "phases must be 1 (push), 2 (GEMM) or 3 (both)");
+    return dk::ag_gemm_impl(A, Bt, C, M, N, K, workspace, view, seq, phases, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dk_ag_gemm(const void* A, const void* Bt, void* C, int M, int N, int K, void* workspace,
+                          const dk_view* view, void* stream) {
+    unsigned seq = 1;
+    if (view != nullptr && view->world > 1) {
+        dk_heap* h = static_cast<dk_heap*>(view->heap);
+        DK_REQUIRE(h != nullptr, "view has no heap handle; use dk_ag_gemm_phase with explicit sequence numbers");
+        DK_REQUIRE(workspace != nullptr && dk::in_heap(view, workspace, dk::ag_gemm_workspace_bytes(M, K, view->world)),
+                   "workspace must lie inside the symmetric heap");
+        if (const int pending = dk::device_status_pending()) return pending;
+        std::lock_guard<std::mutex> lk(h->mu);
+        auto it = h->rs_seq.find(workspace);
+        DK_REQUIRE(it != h->rs_seq.end(), "workspace was not initialised with dk_ag_gemm_workspace_init");
+        seq = ++it->second;
+    }
+    return dk::ag_gemm_impl(A, Bt, C, M, N, K, workspace, view, seq, 3, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dk_ag_gemm_workspace_get(const dk_view* view, int M, int K, void* stream, void** out) {
+    DK_REQUIRE(out != nullptr, "null result pointer");
+    *out = nullptr;
+    if (view == nullptr || view->world <= 1) return DK_OK;
+    dk_heap* h = static_cast<dk_heap*>(view->heap);
+    DK_REQUIRE(h != nullptr, "view has no heap handle");
+    DK_REQUIRE(M > 0 && K > 0 && M % (view->world * dk::BM) == 0, "M must be a positive multiple of world * 128");
+    {
+        std::lock_guard<std::mutex> lk(h->mu);
+        auto it = h->ag_ws.find({M, K});
+        if (it != h->ag_ws.end()) {
+            *out = it->second;
+            return DK_OK;
+        }
+    }
+    const size_t bytes = dk::ag_gemm_workspace_bytes(M, K, view->world);
+    void* ws = dk_heap_alloc(h, bytes, 1024);
+    if (ws == nullptr) {
+        dk::set_last_error("symmetric heap exhausted: an all-gather workspace of " + std::to_string(bytes) +
+                           " bytes does not fit");
+        return DK_ERR_NOMEM;
+    }
+    const int rc = dk_ag_gemm_workspace_init(ws, bytes, view, stream);
+    if (rc != DK_OK) return rc;
+    std::lock_guard<std::mutex> lk(h->mu);
+    h->ag_ws[{M, K}] = ws;
+    *out = ws;
+    return DK_OK;
+}
 
 extern "C" int dk_gemm_pair_mode(int mode) {
     if (mode != 0 && mode != 1) {

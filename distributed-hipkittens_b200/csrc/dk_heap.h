@@ -42,6 +42,7 @@ struct dk_heap {
     std::map<size_t, size_t> used_blocks;  // offset -> size
     std::map<void*, unsigned> rs_seq;      // per GEMM+RS workspace: calls made so far
     std::map<std::pair<int, int>, void*> rs_ws;  // workspaces the heap owns, by (M, N); they die with it
+    std::map<std::pair<int, int>, void*> ag_ws;  // the same for all-gather + GEMM, by (M, K)
 };
 
 namespace dk {

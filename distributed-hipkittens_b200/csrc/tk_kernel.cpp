@@ -129,6 +129,26 @@ void gemm_rs(py::object A, py::object Bt, py::object Out, py::object view) {
     throw_on(dk_gemm_rs(a.ptr, b.ptr, o.ptr, M, N, Kloc, ws, v, stream), "gemm_rs");
 }
 
+// Column-parallel GEMM fused with the all-gather of its activations (dk_ag_gemm): every rank passes
+// its row shard of A and its own columns of the weight and gets all rows of its output columns.
+void ag_gemm(py::object A, py::object Bt, py::object Cout, py::object view) {
+    TensorArg a = tensor_arg(A, "torch.bfloat16");
+    TensorArg b = tensor_arg(Bt, "torch.bfloat16");
+    TensorArg c = tensor_arg(Cout, "torch.bfloat16");
+    if (a.shape.size() != 2 || b.shape.size() != 2 || c.shape.size() != 2)
+        throw std::runtime_error("ag_gemm expects 2-D tensors A[M/P,K], Bt[N,K], C[M,N]");
+    const dk_view* v = view_arg(view);
+    const int world = v ? v->world : 1;
+    const int M = static_cast<int>(a.shape[0]) * world, K = static_cast<int>(a.shape[1]);
+    const int N = static_cast<int>(b.shape[0]);
+    if (b.shape[1] != K) throw std::runtime_error("A and Bt disagree on K");
+    if (c.shape[0] != M || c.shape[1] != N) throw std::runtime_error("C must be [M/P * world, N]");
+    void* ws = nullptr;
+    void* stream = current_stream();
+    throw_on(dk_ag_gemm_workspace_get(v, M, K, stream, &ws), "ag_gemm workspace");
+    throw_on(dk_ag_gemm(a.ptr, b.ptr, c.ptr, M, N, K, ws, v, stream), "ag_gemm");
+}
+
 void allreduce(py::object X, py::object Out, py::object view, int algo) {
     TensorArg x = tensor_arg(X, "torch.bfloat16");
     TensorArg o = tensor_arg(Out, "torch.bfloat16");
@@ -402,6 +422,8 @@ PYBIND11_MODULE(tk_kernel, m) {
           "C[M,N] = A[M,K] @ Bt[N,K]^T (bf16, fp32 accumulate), the single-GPU form. Positional: A, Bt, C");
     m.def("gemm_rs", &gemm_rs,
           "Out[M/P,N] = reduce-scatter over ranks of A[M,K/P] @ Bt[N,K/P]^T. Positional: A, Bt, Out, view");
+    m.def("ag_gemm", &ag_gemm,
+          "C[M,N] = (all-gather over ranks of A[M/P,K]) @ Bt[N,K]^T, gather fused into the GEMM. Positional: A, Bt, C, view");
     m.def("allreduce", &allreduce, py::arg("X"), py::arg("Out"), py::arg("view"), py::arg("algo") = -1,
           "Out = sum over ranks of X (bf16). algo: -1 auto, 0 one-shot, 1 two-shot, 2 NVLS");
     m.def("moe_route", &moe_route, "(topk_idx int32 [T,k], topk_w fp32 [T,k]) from fp32 logits [T,E]");

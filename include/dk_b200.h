@@ -176,6 +176,32 @@ int dk_gemm_rs_phase(const void* A, const void* Bt, void* out, int M, int N, int
 /* (`epilogue` is honoured for world == 1 only: pushes to peers always use TMA bulk stores.) */
 
 /*
+ * Column-parallel GEMM fused with the all-gather of its activations, no NCCL: the projection that
+ * precedes the row-parallel one of dk_gemm_rs in a tensor-parallel MLP.
+ *   C[M, N] (all rows, this rank's N columns) = concat over ranks r of A_r[M/P, K]  *  Bt[N, K]^T
+ * Every rank calls it with its own row shard A_r and its own weight columns Bt. Inside ONE kernel,
+ * the warps a plain GEMM leaves idle push the shard to every peer's staging copy of A (16-byte peer
+ * stores, a per-tile counter at the destination), while the MMA warps start on the rank's own rows
+ * and take the other shards in the order rank+1, rank+2, ... as their tiles complete; TMA only ever
+ * loads from this GPU's own memory. M % (world*128) == 0. The reference has no counterpart (it has
+ * no collective); calling convention and operand layouts are those of dispatch_micro.
+ *
+ * `workspace`: dk_ag_gemm_workspace_bytes(M, K, world) bytes from the symmetric heap at the same
+ * offset on every rank, initialised once, collectively, with dk_ag_gemm_workspace_init (or taken
+ * from the heap with dk_ag_gemm_workspace_get, which does both on first use and keeps it with the
+ * heap). With world == 1 the call is a plain GEMM and workspace may be NULL. dk_ag_gemm_phase runs
+ * the push (bit 0) and the GEMM (bit 1) as separate launches with an explicit 1-based call number,
+ * for running all ranks of a job on one GPU.
+ */
+size_t dk_ag_gemm_workspace_bytes(int M, int K, int world);
+int dk_ag_gemm_workspace_init(void* workspace, size_t bytes, const dk_view* view, void* stream);
+int dk_ag_gemm_workspace_get(const dk_view* view, int M, int K, void* stream, void** out);
+int dk_ag_gemm(const void* A_shard, const void* Bt, void* C, int M, int N, int K, void* workspace,
+               const dk_view* view, void* stream);
+int dk_ag_gemm_phase(const void* A_shard, const void* Bt, void* C, int M, int N, int K, void* workspace,
+                     const dk_view* view, unsigned seq, int phases, void* stream);
+
+/*
  * Mode 1 (the default; DK_GEMM_PAIR=0 in the environment selects 0) makes dk_gemm_bf16 / dk_gemm_rs
  * use clusters of two CTAs per 256x256 tile (tcgen05.mma.cta_group::2: each CTA stages its 128
  * rows of A and half of the Bt tile in a six-stage ring, both CTAs' TMA loads complete on the

@@ -44,6 +44,23 @@ def _worker(rank, world, job, q):
             errs.append(orc.rel_fro(out.float().cpu(), want))
         res["gemm_rs"] = errs
 
+        # ---- all-gather + GEMM: every rank's row shard against this rank's own weight columns
+        Ma, Na, Ka = 256 * world, 264, 512
+        Afull, _ = orc.make_gemm_inputs(Ma, 8, Ka, seed=40)
+        Bcol = orc.make_gemm_inputs(8, Na, Ka, seed=41 + rank)[1]
+        want_ag = orc.gemm_ref(Afull, Bcol)
+        sh = Ma // world
+        dAs, dBc = Afull[rank * sh:(rank + 1) * sh].contiguous().cuda(), Bcol.cuda()
+        out_ag = torch.empty(Ma, Na, dtype=torch.bfloat16, device="cuda")
+        errs = []
+        for _ in range(3):
+            out_ag.fill_(float("nan"))
+            iris.barrier()
+            tk_kernel.ag_gemm(dAs, dBc, out_ag, view)
+            torch.cuda.synchronize()
+            errs.append(orc.rel_fro(out_ag.float().cpu(), want_ag))
+        res["ag_gemm"] = errs
+
         # ---- all-reduce, one-shot and two-shot
         shape = (64, 8192)
         xs = orc.make_allreduce_inputs(shape, world)
@@ -177,6 +194,7 @@ def test_peer_memory_path(world):
         assert "error" not in results[r], results[r].get("error")
         assert results[r]["status"][0] == 0
         assert all(e <= 1e-2 for e in results[r]["gemm_rs"]), results[r]["gemm_rs"]
+        assert all(e <= 1e-2 for e in results[r]["ag_gemm"]), results[r]["ag_gemm"]
         assert results[r]["moe_idx_ok"]
         assert all(e <= 2e-2 for e in results[r]["moe_ep"]), results[r]["moe_ep"]
         assert all(e <= 2e-2 for e in results[r]["moe_layer"]), results[r]["moe_layer"]
