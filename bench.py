@@ -388,6 +388,77 @@ class AgGemm:
         return r
 
 
+class MxGemm:
+    """MXFP8 GEMM 8192^3 (e4m3 with one e8m0 scale per 1x32 block, scales applied by the tensor core):
+    the shape the reference's GEMM benchmarks use (kernels/cdna4/gemm/mxfp8, analysis/fp8_gemm)."""
+    metric, unit, dtype, scaling = "gemm_mxfp8_tflops", "TFLOP/s", "fp8_e4m3", "weak"
+    launches_per_step = 1
+    M = N = K = 8192
+
+    def __init__(self, ctx):
+        import torch
+        self.ctx = ctx
+        g = torch.Generator(device="cuda").manual_seed(3000 + ctx.rank)
+        self.sets = []
+        for _ in range(3):          # 3 x 134 MB of operands rotated: more than L2 between two uses
+            a = torch.randn(self.M, self.K, device="cuda", generator=g).to(torch.bfloat16)
+            b = (torch.randn(self.N, self.K, device="cuda", generator=g) / math.sqrt(self.K)).to(torch.bfloat16)
+            aq, sa, asf = ctx.capi.mx_quant(a)
+            bq, sb, bsf = ctx.capi.mx_quant(b)
+            self.sets.append((aq, asf, bq, bsf))
+            self.rowmajor = (sa, sb)          # scales of the last set, row-major, for check()
+        self.a_bf16 = a
+        self.work = 2.0 * self.M * self.N * self.K * ctx.world
+        self.scale = 1e12
+
+    def step(self, i):
+        aq, asf, bq, bsf = self.sets[i % 3]
+        self.out = self.ctx.tk.gemm_mxfp8(aq, asf, bq, bsf)
+
+    def quant_gbs(self):
+        """The quantiser alone: 2 bytes read + 1 written per element (+ scales)."""
+        import torch
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(3):
+            self.ctx.capi.mx_quant(self.a_bf16)
+        e0.record()
+        for _ in range(10):
+            self.ctx.capi.mx_quant(self.a_bf16)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / 10
+        return self.M * self.K * (3 + 1.0 / 32 + 4.0 / 128) / (ms * 1e-3) / 1e9
+
+    def check(self):
+        """64 rows of the fp32-output GEMM against torch on the dequantised operands."""
+        import torch
+        aq, asf, bq, bsf = self.sets[2]
+        sa, sb = self.rowmajor
+        out = self.ctx.tk.gemm_mxfp8(aq, asf, bq, bsf, True)
+        torch.cuda.synchronize()
+
+        def deq(q, sc):
+            f = torch.ldexp(torch.ones_like(sc, dtype=torch.float32), sc.to(torch.int32) - 127)
+            return q.view(torch.float8_e4m3fn).float() * f.repeat_interleave(32, dim=1)
+        ref = deq(aq[:64], sa[:64]) @ deq(bq, sb).T
+        return self.ctx.max_over_ranks(((out[:64] - ref).norm() / ref.norm()).item())
+
+    def e2e_setup(self):
+        return None
+
+    def config(self, value):
+        return {"workload": f"MXFP8 GEMM {self.M}x{self.N}x{self.K} per GPU (e4m3, 1x32 e8m0 scales applied by the "
+                            f"block-scaled MMA), bf16 out", "l2": "3 operand sets of 134 MB rotated",
+                "per_gpu_tflops": value / self.ctx.world}
+
+    def roofline(self, ms_step, sustained, peaks, peak_src):
+        bf16 = peaks.get("bf16_tflops_sustained" if sustained else "bf16_tflops")
+        ach = 2.0 * self.M * self.N * self.K / (ms_step * 1e-3) / 1e12
+        return {"bound": "tensor", "achieved": ach, "peak": 2.0 * bf16 if bf16 else None, "unit": "TFLOP/s",
+                "frac": ach / (2.0 * bf16) if bf16 else None, "frac_of_nominal_4500": ach / 4500.0, "traffic": None,
+                "peak_source": f"2 x {peak_src} cuBLAS bf16 ({'sustained' if sustained else 'burst'}) taken as the fp8 dense peak"}
+
+
 class AllReduce:
     """TP all-reduce of bf16 activations: decode [64 x 8192] (1 MiB) and prefill [8192 x 8192]
     (128 MiB); a step is one all-reduce of each."""
@@ -826,6 +897,20 @@ def ag_gemm_secondary(ctx, peaks, peak_src):
     return e
 
 
+def mx_gemm_secondary(ctx, peaks, peak_src):
+    wl = MxGemm(ctx)
+    ms, _ = time_steps(ctx, wl, steps=20, warmup=5)
+    err = wl.check()
+    r = wl.roofline(ms, False, peaks, peak_src)
+    e = {"workload": wl.config(0.0)["workload"], "step_ms": ms, "tflops_per_gpu": r["achieved"], "roofline": r,
+         "quantiser_hbm_gbs": wl.quant_gbs(), "quantiser_frac_of_measured_hbm": None, "check_rel_fro": err}
+    if peaks.get("hbm_gbs"):
+        e["quantiser_frac_of_measured_hbm"] = e["quantiser_hbm_gbs"] / peaks["hbm_gbs"]
+    assert err <= 1e-3, f"MXFP8 GEMM differs from the dequantised torch reference by {err}"
+    del wl
+    return e
+
+
 def allreduce_secondary(ctx):
     wl = AllReduce(ctx)
     ms, _ = time_steps(ctx, wl, steps=10, warmup=3)
@@ -844,6 +929,126 @@ def allreduce_secondary(ctx):
     return e
 
 
+def run_emulated(args, out):
+    """--emulate-ranks P: the multi-rank kernels with all P ranks on ONE GPU (every rank's heap is a
+    region of one buffer; phases run rank after rank, the all-reduce as one cooperative launch), for
+    profiling them where only one GPU can be profiled. Not a benchmark of the metric: NVLink is not
+    involved, the figures are HBM-side. Prints one JSON line with the per-phase times."""
+    import torch
+    from __graft_entry__ import load_package
+    capi = load_package().capi
+    P, steps, warm = args.emulate_ranks, args.steps, max(args.warmup, 3)
+    torch.cuda.set_device(0)
+
+    def job(ws_bytes):
+        region = capi.CTRL_BYTES + (ws_bytes + 4095) // 4096 * 4096
+        buf = torch.zeros(P * region + 4096, dtype=torch.uint8, device="cuda")
+        base0 = (buf.data_ptr() + 1023) // 1024 * 1024
+        bases = [base0 + r * region for r in range(P)]
+        return buf, [capi.make_view(r, P, bases, region) for r in range(P)], [b + capi.CTRL_BYTES for b in bases]
+
+    def timed(fn, first_seq=1):
+        seq = first_seq
+        for _ in range(warm):
+            fn(seq)
+            seq += 1
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn(seq)
+            seq += 1
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps, seq
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    res = {"emulated_ranks": P, "workload": args.workload, "steps": steps}
+    if args.workload == "allreduce":
+        n = (args.tokens or 4096) * 4096                      # bf16 elements per rank (32 MiB by default)
+        buf, views, ws = job(2 * n * 2 + 8192)
+        xs = [capi.tensor_from_ptr(w, (n,), torch.bfloat16) for w in ws]
+        outs = [capi.tensor_from_ptr(w + n * 2 + 4096, (n,), torch.bfloat16) for w in ws]
+        for x in xs:
+            x.copy_(torch.randn(n, device="cuda", generator=g).to(torch.bfloat16))
+        seq = 1
+        for algo, name in ((0, "oneshot"), (1, "twoshot")):
+            ms, seq = timed(lambda s_, a=algo: capi.allreduce_all_ranks(views, xs, outs, a, s_), seq)
+            res[f"{name}_ms"] = ms
+            # every rank reads P inputs and writes one output (one-shot) / reads P slices, writes P slices
+            res[f"{name}_hbm_gbs"] = (P * (P + 1) * n * 2 if algo == 0 else P * 2 * n * 2) / (ms * 1e-3) / 1e9
+        res["bytes_per_rank"] = n * 2
+    elif args.workload in ("gemm_rs", "ag_gemm"):
+        M, N, K = (M_TOK, N_OUT, K_FULL) if args.shape else ((8192, 8192, 28672) if args.workload == "gemm_rs"
+                                                             else (8192, 28672, 8192))
+        if args.workload == "gemm_rs":
+            Kl = K // P
+            buf, views, ws = job(capi.gemm_rs_workspace_bytes(M, N, P))
+            A = [torch.randn(M, Kl, device="cuda", generator=g).to(torch.bfloat16) for _ in range(P)]
+            B = [(torch.randn(N, Kl, device="cuda", generator=g) / math.sqrt(K)).to(torch.bfloat16) for _ in range(P)]
+            O = [torch.empty(M // P, N, dtype=torch.bfloat16, device="cuda") for _ in range(P)]
+            call = lambda r, s_, ph: capi.gemm_rs_phase(A[r], B[r], O[r], ws[r], views[r], s_, ph)
+            names = ("produce", "reduce")
+        else:
+            Nl = N // P
+            buf, views, ws = job(capi.ag_gemm_workspace_bytes(M, K, P))
+            A = [torch.randn(M // P, K, device="cuda", generator=g).to(torch.bfloat16) for _ in range(P)]
+            B = [(torch.randn(Nl, K, device="cuda", generator=g) / math.sqrt(K)).to(torch.bfloat16) for _ in range(P)]
+            O = [torch.empty(M, Nl, dtype=torch.bfloat16, device="cuda") for _ in range(P)]
+            call = lambda r, s_, ph: capi.ag_gemm_phase(A[r], B[r], O[r], ws[r], views[r], s_, ph)
+            names = ("push", "gemm")
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        acc = [0.0, 0.0]
+        for it in range(warm + steps):
+            seq = it + 1
+            ev[0].record()
+            for r in range(P):
+                call(r, seq, 1)
+            ev[1].record()
+            for r in range(P):
+                call(r, seq, 2)
+            ev[2].record()
+            torch.cuda.synchronize()
+            if it >= warm:
+                acc[0] += ev[0].elapsed_time(ev[1]) / steps
+                acc[1] += ev[1].elapsed_time(ev[2]) / steps
+        res.update({f"{names[0]}_ms_all_ranks": acc[0], f"{names[1]}_ms_all_ranks": acc[1], "shape": [M, N, K]})
+    else:
+        sh = dict(Moe.SHAPES[args.workload])
+        T, H, F, k = args.tokens or 4096, sh["H"], sh["F"], sh["k"]
+        E = args.experts or sh["E"]
+        epr, Tl = E // P, T // P
+        pow2 = args.scales == "pow2"
+        buf, views, ws = job(capi.moe_ep_workspace_bytes(Tl, k, E, H, F, P))
+        ranks = []
+        for r in range(P):
+            w13 = [(capi.quant_block128_pow2 if pow2 else capi.quant_block128)(
+                (torch.randn(2 * F, H, device="cuda", generator=g) / math.sqrt(H)).to(torch.bfloat16)) for _ in range(epr)]
+            w2 = [(capi.quant_block128_pow2 if pow2 else capi.quant_block128)(
+                (torch.randn(H, F, device="cuda", generator=g) / math.sqrt(F)).to(torch.bfloat16)) for _ in range(epr)]
+            si = 3 if pow2 else 1
+            s13, s2 = torch.stack([w[si] for w in w13]), torch.stack([w[si] for w in w2])
+            if pow2:
+                s13, s2 = s13.reshape(-1, s13.shape[-2], 512), s2.reshape(-1, s2.shape[-2], 512)
+            ranks.append(dict(x=torch.randn(Tl, H, device="cuda", generator=g).to(torch.bfloat16),
+                              logits=torch.randn(Tl, E, device="cuda", generator=g),
+                              w13q=torch.stack([w[0] for w in w13]), w13s=s13,
+                              w2q=torch.stack([w[0] for w in w2]), w2s=s2,
+                              out=torch.empty(Tl, H, dtype=torch.bfloat16, device="cuda")))
+
+        def layer(seq):
+            for ph in (1, 2, 4, 8):
+                for r, d in enumerate(ranks):
+                    capi.moe_ep_layer(d["x"], d["logits"], d["w13q"], d["w13s"], d["w2q"], d["w2s"], d["out"], ws[r],
+                                      views[r], k, scale_mode=1 if pow2 else 0, epoch=seq, phases=ph)
+        ms, _ = timed(layer)
+        res.update({"layer_ms_all_ranks": ms, "tokens": T, "experts": E, "H": H, "F": F, "k": k, "scales": args.scales})
+    st = capi.device_status()
+    assert st[0] == 0, f"device-side error record: {st}"
+    out.write(json.dumps(res) + "\n")
+    out.flush()
+
+
 def main():
     out = _claim_stdout()
     ap = argparse.ArgumentParser()
@@ -852,7 +1057,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gemm_rs",
-                    choices=["gemm_rs", "ag_gemm", "allreduce", "moe_mixtral", "moe_dsv3"])
+                    choices=["gemm_rs", "ag_gemm", "gemm_mxfp8", "allreduce", "moe_mixtral", "moe_dsv3"])
     ap.add_argument("--scales", default="fp32", choices=["fp32", "pow2"],
                     help="MoE workloads: fp32 128x128 block scales (software promotion) or power-of-two "
                          "block scales applied by the block-scaled MMA")
@@ -866,6 +1071,9 @@ def main():
                     help="compare one result with a NCCL/torch reference outside the timed region "
                          "(always done when more than one GPU is used)")
     ap.add_argument("--tokens", type=int, default=0, help="token-count override of a MoE workload (profiling runs)")
+    ap.add_argument("--experts", type=int, default=0, help="expert-count override with --emulate-ranks (profiling runs)")
+    ap.add_argument("--emulate-ranks", type=int, default=0,
+                    help="profiling runs: all ranks of a P-rank job on one GPU, phase by phase (see run_emulated)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 0)
 
@@ -877,6 +1085,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", str(rank)))
     if args.impl == "reference":
         run_reference(args, rank, out)
+        return
+    if args.emulate_ranks:
+        assert world == 1, "--emulate-ranks runs on one GPU"
+        run_emulated(args, out)
         return
 
     import torch
@@ -892,7 +1104,8 @@ def main():
     ctx = Ctx(rank, world, local_rank)
     secondary_on = args.workload == "gemm_rs" and not args.no_secondary and not args.shape
     # one symmetric heap for everything this run will do
-    need = {"gemm_rs": GemmRs.heap_mb(world), "ag_gemm": AgGemm.heap_mb(world), "allreduce": AllReduce.HEAP_MB}
+    need = {"gemm_rs": GemmRs.heap_mb(world), "ag_gemm": AgGemm.heap_mb(world), "allreduce": AllReduce.HEAP_MB,
+            "gemm_mxfp8": 64}
     for wname in ("moe_mixtral", "moe_dsv3"):
         need[wname] = Moe.heap_mb(ctx, wname, args.tokens if args.workload == wname else 0)
     heap_mb = need[args.workload] + (sum(v for k_, v in need.items() if k_ != args.workload) if secondary_on else 0)
@@ -902,6 +1115,8 @@ def main():
         wl = GemmRs(ctx)
     elif args.workload == "ag_gemm":
         wl = AgGemm(ctx)
+    elif args.workload == "gemm_mxfp8":
+        wl = MxGemm(ctx)
     elif args.workload == "allreduce":
         wl = AllReduce(ctx)
     else:
@@ -1018,6 +1233,7 @@ def main():
         torch.cuda.empty_cache()
         sec = {}
         sec["ag_gemm"] = ag_gemm_secondary(ctx, peaks, peak_src)
+        sec["gemm_mxfp8"] = mx_gemm_secondary(ctx, peaks, peak_src)
         if world > 1:
             sec["allreduce"] = allreduce_secondary(ctx)
         for which in ("moe_mixtral", "moe_dsv3"):

@@ -5,6 +5,7 @@ repository's `__graft_entry__.py`) under the module name `distributed_hipkittens
 
   capi        ctypes binding of libdk_b200.so, the C ABI in include/dk_b200.h
   build       in-tree build of the library and of the pybind11 modules `iris_py` / `tk_kernel`
+  torch_ops   torch.library operators (torch.ops.dk_b200.*) over the tk_kernel entry points; imported on demand
 """
 from . import capi  # noqa: F401
 
