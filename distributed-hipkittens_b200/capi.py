@@ -113,6 +113,7 @@ def _declare(L: C.CDLL) -> None:
     L.dk_moe_permute_static.argtypes = [vp, i, i, i, i, i, vp, vp, i, vp, vp, vp]
     L.dk_moe_combine.argtypes = [vp, vp, vp, i, i, i, vp, vp]
     L.dk_moe_grouped_gemm_fp8.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, vp, vp, vp]
+    L.dk_mx_pair_mode.argtypes = [i]
     L.dk_mx_sf_bytes.restype = sz
     L.dk_mx_sf_bytes.argtypes = [i, i]
     L.dk_mx_quant.argtypes = [vp, i, i, i, vp, vp, vp, vp]

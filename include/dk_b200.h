@@ -365,6 +365,13 @@ int dk_gemm_mxfp8(const void* aq, const void* sfa, const void* bq, const void* s
  * writes e4m3 bytes [R, N] of silu(gate) * up requantised per 128x128 block with a power-of-two
  * scale, out_e8 [R/128, N/128] and out_atoms [R/128][ceil(N/512)][512]; gated = 0 writes bf16 [R, N].
  */
+/*
+ * Mode 1 (DK_MX_PAIR=1 in the environment) runs dk_gemm_mxfp8 and dk_moe_grouped_gemm_mxfp8 with
+ * clusters of two CTAs per 256-row tile (tcgen05 cta_group::2: half the shared-memory fill per flop,
+ * a six-stage ring); mode 0 (the default: it measured as fast on large GEMMs and faster on many
+ * small experts) with one CTA per 128-row tile. Results are identical. No reference counterpart.
+ */
+int dk_mx_pair_mode(int mode);
 int dk_quant_block128_pow2(const void* x, int R, int C, const int* row_map, int map_mode, int k, void* q,
                            float* s, void* e8, void* sf_atoms, void* stream);
 int dk_moe_grouped_gemm_mxfp8(const void* xq, const void* x_atoms, const void* wq, const void* w_atoms,
