@@ -41,8 +41,10 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float* __restrict_
         v[i] = e < E ? row[e] : -INFINITY;
         taken[i] = e >= E;
     }
-    float sel_v[ROUTE_MAX_K];
-    int sel_e[ROUTE_MAX_K];
+    // lane j keeps the j-th selection (no dynamically indexed arrays, and the results are written by
+    // k lanes at once instead of one lane after the other)
+    float my_v = -INFINITY, top_v = 0.f;
+    int my_e = 0;
 #pragma unroll 1
     for (int j = 0; j < k; ++j) {
         // best of this lane: largest value, lowest index among equals (ascending scan, strict >)
@@ -68,30 +70,28 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float* __restrict_
                 be = oe;
             }
         }
-        sel_v[j] = bv;
-        sel_e[j] = be;
+        if (j == 0) top_v = bv;
+        if (lane == j) {
+            my_v = bv;
+            my_e = be;
+        }
         if ((be & 31) == lane) {
 #pragma unroll
             for (int i = 0; i < ROUTE_MAX_E / 32; ++i)
                 if (lane + 32 * i == be) taken[i] = true;
         }
     }
-    if (lane == 0) {
-        // renormalised softmax over the selection: the full-softmax denominator cancels
-        const float m = sel_v[0];
-        float p[ROUTE_MAX_K];
-        float sum = 0.f;
-        for (int j = 0; j < k; ++j) {
-            p[j] = expf(sel_v[j] - m);
-            sum += p[j];
-        }
-        for (int j = 0; j < k; ++j) {
-            const size_t at = static_cast<size_t>(out.row_base + warp) * k + j;
-            const float wj = p[j] / sum;
-            for (int r = 0; r < out.n_out; ++r) {
-                out.idx[r][at] = sel_e[j];
-                out.w[r][at] = wj;
-            }
+    // renormalised softmax over the selection: the full-softmax denominator cancels. The sum is
+    // formed in slot order, as a serial loop would, so the bits do not depend on the lane count.
+    const float p = lane < k ? expf(my_v - top_v) : 0.f;
+    float sum = 0.f;
+    for (int j = 0; j < k; ++j) sum += __shfl_sync(0xffffffffu, p, j);
+    if (lane < k) {
+        const size_t at = static_cast<size_t>(out.row_base + warp) * k + lane;
+        const float wj = p / sum;
+        for (int r = 0; r < out.n_out; ++r) {
+            out.idx[r][at] = my_e;
+            out.w[r][at] = wj;
         }
     }
     }
