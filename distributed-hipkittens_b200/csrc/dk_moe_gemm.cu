@@ -177,7 +177,10 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
     // compiled for (a spill in the K loop costs more than anything else in this kernel), while the
     // TMA and MMA warps need a few dozen.
     // (Each setmaxnreg sits at the head of the branch it governs: placed before a join it would
-    // bind the code after the join to the smaller value.)
+    // bind the code after the join to the smaller value. The increase can only draw on what this
+    // CTA's own warps gave back: 128 x (168 - 40) = 256 x (232 - 168); asking for more blocks for ever.)
+    // Tried and measured slower: sixteen promotion warps (four per lane quarter, 64 accumulators and one
+    // 32-column load in flight each, 112 registers): Mixtral-shape GEMMs 1419 against 1709 TFLOP/s.
     if (warp < 4) {
       asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
       if (warp == 0) {
