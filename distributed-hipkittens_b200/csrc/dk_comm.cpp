@@ -6,6 +6,12 @@
 // other rank's heap. Here: rank and world come from the environment, ranks meet on an abstract
 // Unix-domain socket (star around rank 0), file descriptors travel with SCM_RIGHTS.
 // Pure host code with no CUDA in it, so it is testable on a machine without a GPU.
+//
+// Who may join: the socket name is predictable, and whoever joins receives the descriptors of every
+// rank's heap. Rank 0 therefore accepts a connection only from a process of its own user
+// (SO_PEERCRED) whose hello carries the job's token (DK_JOB_TOKEN in the environment of all ranks; 0
+// when unset); connections are accepted at once and their hello read when it arrives, so a silent
+// connection holds up nobody; anything else is dropped without giving up the job.
 #include <errno.h>
 #include <poll.h>
 #include <stdlib.h>
@@ -16,6 +22,7 @@
 #include <unistd.h>
 
 #include <atomic>
+#include <cstdint>
 #include <string>
 #include <vector>
 
@@ -158,11 +165,36 @@ socklen_t make_addr(const std::string& name, sockaddr_un* a) {
 
 std::atomic<int> g_comm_seq{0};
 
+struct Hello {
+    int32_t rank;
+    uint32_t magic;
+    uint64_t token;
+};
+constexpr uint32_t HELLO_MAGIC = 0x646b3230u;
+
+// FNV-1a of DK_JOB_TOKEN (0 when unset): ranks of one job share it through their environment.
+uint64_t job_token() {
+    const char* t = getenv("DK_JOB_TOKEN");
+    if (t == nullptr || *t == '\0') return 0;
+    uint64_t h = 1469598103934665603ull;
+    for (; *t; ++t) h = (h ^ static_cast<unsigned char>(*t)) * 1099511628211ull;
+    return h ? h : 1;
+}
+
+bool same_user(int s) {
+    ucred cr{};
+    socklen_t len = sizeof(cr);
+    if (getsockopt(s, SOL_SOCKET, SO_PEERCRED, &cr, &len) != 0) return false;
+    return cr.uid == geteuid();
+}
+
+// Empty when neither DK_JOB_ID nor MASTER_PORT names the job (two jobs of one host would otherwise
+// meet on the same default name).
 std::string default_rendezvous() {
     std::string base;
     if (const char* e = getenv("DK_JOB_ID")) base = e;
     else if (const char* p = getenv("MASTER_PORT")) base = std::string("port") + p;
-    else base = "default";
+    else return std::string();
     // heaps are created in the same order on every rank, so a per-process counter pairs them up
     return base + "." + std::to_string(g_comm_seq.fetch_add(1));
 }
@@ -204,6 +236,14 @@ int dk_comm_create(int rank, int world, const char* rendezvous, int timeout_ms, 
     if (world == 1) return DK_OK;
 
     const std::string name = (rendezvous && *rendezvous) ? rendezvous : default_rendezvous();
+    if (name.empty()) {
+        errno = 0;
+        int rc = fail("no rendezvous name: pass one, or set DK_JOB_ID (or MASTER_PORT, as torchrun does) in the "
+                      "environment of every rank");
+        delete c; *out = nullptr;
+        return rc;
+    }
+    const uint64_t token = job_token();
     sockaddr_un addr;
     const socklen_t alen = make_addr(name, &addr);
     const int64_t deadline = now_ms() + c->timeout_ms;
@@ -218,26 +258,55 @@ int dk_comm_create(int rank, int world, const char* rendezvous, int timeout_ms, 
             close(c->listen_fd); delete c; *out = nullptr;
             return rc;
         }
+        // Connections are accepted at once and their hello is read when it arrives, so a connection
+        // that says nothing holds up nobody. A stranger (other user), a wrong token or magic, a rank
+        // out of range or already here: dropped, and the loop goes on waiting for the real ranks.
+        std::vector<int> pending;
+        auto drop_pending = [&]() {
+            for (int fd : pending) close(fd);
+            pending.clear();
+        };
         for (int got = 0; got < world - 1;) {
-            int left = static_cast<int>(deadline - now_ms());
-            if (left <= 0 || !wait_fd(c->listen_fd, POLLIN, left)) {
+            const int left = static_cast<int>(deadline - now_ms());
+            std::vector<pollfd> pf;
+            pf.push_back({c->listen_fd, POLLIN, 0});
+            for (int fd : pending) pf.push_back({fd, POLLIN, 0});
+            const int pr = left > 0 ? poll(pf.data(), pf.size(), left) : 0;
+            if (pr < 0 && errno == EINTR) continue;
+            if (pr <= 0) {
                 errno = ETIMEDOUT;
                 int rc = fail("timed out waiting for " + std::to_string(world - 1 - got) +
                               " rank(s) at rendezvous '" + name + "'");
+                drop_pending();
                 dk_comm_destroy(c); *out = nullptr;
                 return rc;
             }
-            int s = accept4(c->listen_fd, nullptr, nullptr, SOCK_CLOEXEC);
-            if (s < 0) continue;
-            int32_t r = -1;
-            if (!recv_all(s, &r, sizeof(r), c->timeout_ms) || r <= 0 || r >= world ||
-                c->peers[r] != -1) {
-                close(s);
-                continue;
+            std::vector<int> still;
+            for (size_t i = 1; i < pf.size(); ++i) {
+                const int s = pf[i].fd;
+                if ((pf[i].revents & (POLLIN | POLLHUP | POLLERR)) == 0) {
+                    still.push_back(s);
+                    continue;
+                }
+                Hello h{-1, 0, 0};
+                if (!recv_all(s, &h, sizeof(h), 1000) || h.magic != HELLO_MAGIC || h.token != token || h.rank <= 0 ||
+                    h.rank >= world || c->peers[h.rank] != -1) {
+                    close(s);
+                    continue;
+                }
+                c->peers[h.rank] = s;
+                ++got;
             }
-            c->peers[r] = s;
-            ++got;
+            pending.swap(still);
+            if (pf[0].revents & POLLIN) {
+                const int s = accept4(c->listen_fd, nullptr, nullptr, SOCK_CLOEXEC);
+                if (s >= 0) {
+                    if (same_user(s)) pending.push_back(s);
+                    else close(s);
+                }
+            }
         }
+        drop_pending();
     } else {
         c->peers.assign(1, -1);
         for (;;) {
@@ -256,8 +325,8 @@ int dk_comm_create(int rank, int world, const char* rendezvous, int timeout_ms, 
             }
             usleep(5000);
         }
-        int32_t r = rank;
-        if (!send_all(c->peers[0], &r, sizeof(r))) {
+        const Hello h{rank, HELLO_MAGIC, token};
+        if (!send_all(c->peers[0], &h, sizeof(h))) {
             int rc = fail("hello to rank 0");
             dk_comm_destroy(c); *out = nullptr;
             return rc;

@@ -178,3 +178,59 @@ def test_comm_missing_rank_times_out_with_an_error():
     rc, msg = q.get(timeout=30)
     p.join(10)
     assert rc == 4 and "timed out" in msg
+
+
+def test_comm_drops_a_connection_with_the_wrong_token_and_still_forms(capi, monkeypatch):
+    """Whoever joins the rendezvous receives the descriptors of every rank's heap, so rank 0 accepts
+    only its own user's processes whose hello carries the job's token (DK_JOB_TOKEN). An intruder with
+    the wrong token (and one that says nothing) is dropped; the job still forms."""
+    import socket
+    import struct
+    import threading
+    monkeypatch.setenv("DK_JOB_TOKEN", "secret-of-this-job")
+    L = capi.lib()
+    name = f"tok{os.getpid()}"
+    res = {}
+
+    def rank(r):
+        h = C.c_void_p()
+        res[r] = L.dk_comm_create(r, 2, name.encode(), 15000, C.byref(h))
+        if res[r] == 0:
+            res[f"b{r}"] = L.dk_comm_barrier(h)
+            L.dk_comm_destroy(h)
+
+    t0 = threading.Thread(target=rank, args=(0,))
+    t0.start()
+    addr = "\0dk_b200." + name
+    silent = None
+    for _ in range(400):                    # wait for rank 0 to listen
+        try:
+            silent = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+            silent.connect(addr)
+            break
+        except OSError:
+            silent.close()
+            silent = None
+            import time
+            time.sleep(0.01)
+    assert silent is not None               # connected, and never says a word
+    bad = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+    bad.connect(addr)
+    bad.sendall(struct.pack("<iIQ", 1, 0x646b3230, 12345))      # rank 1, right magic, wrong token
+    t1 = threading.Thread(target=rank, args=(1,))
+    t1.start()
+    t0.join(30)
+    t1.join(30)
+    assert res.get(0) == 0 and res.get(1) == 0 and res.get("b0") == 0 and res.get("b1") == 0
+    bad.settimeout(2)
+    assert bad.recv(1) == b""               # rank 0 closed the intruder's connection
+    bad.close()
+    silent.close()
+
+
+def test_comm_needs_a_job_name(capi, monkeypatch):
+    for k in ("DK_JOB_ID", "MASTER_PORT"):
+        monkeypatch.delenv(k, raising=False)
+    h = C.c_void_p()
+    assert capi.lib().dk_comm_create(0, 2, None, 500, C.byref(h)) == capi.ERR_BOOTSTRAP
+    assert b"DK_JOB_ID" in capi.lib().dk_last_error_string()
