@@ -129,17 +129,17 @@ static int launch_mx_p(const MxMaps& maps, const MxArgs& g, int max_tiles, cudaS
     return DK_OK;
 }
 
-// -1: read DK_MX_PAIR on first use; 0 one CTA per tile (default); 1 pairs. The pair form moves 30 %
-// fewer bytes through L1/L2 but measured the same tensor-pipe activity (63 %) and the same speed on
-// large GEMMs, and loses on many small experts (odd tile counts leave half a pair idle), so it is
-// offered, tested, and not the default.
-static int g_mx_pair = -1;
-static bool mx_use_pair() {
-    if (g_mx_pair < 0) {
+// -1 (default, or DK_MX_PAIR unset): pairs for the plain GEMM, one CTA per tile for the grouped GEMMs;
+// 0 / 1 (dk_mx_pair_mode, DK_MX_PAIR): one form for both. The pair form moves 30 % fewer bytes
+// through L1/L2; on the plain GEMM it measured 0-5 % faster depending on the board, on many small
+// experts it loses (an odd number of 128-row tiles leaves half a pair idle).
+static int g_mx_pair = -2;
+static bool mx_use_pair(bool grouped) {
+    if (g_mx_pair == -2) {
         const char* e = std::getenv("DK_MX_PAIR");
-        g_mx_pair = (e && *e && std::atoi(e) == 1) ? 1 : 0;
+        g_mx_pair = (e && *e) ? (std::atoi(e) != 0 ? 1 : 0) : -1;
     }
-    return g_mx_pair == 1;
+    return g_mx_pair == 1 || (g_mx_pair == -1 && !grouped);
 }
 
 // [atoms, 128 x u32] view of a scale-atom array for tensor-map loads of whole atoms (no swizzle).
@@ -161,7 +161,7 @@ static int make_atom_map(CUtensorMap* out, const void* base, size_t n_atoms) {
 template <int MODE, bool BLK>
 static int launch_mx(MxMaps& maps, MxArgs& g, const void* aq, int a_rows, const void* bq, uint64_t b_rows_total,
                      int row_tiles_upper, cudaStream_t st) {
-    const bool pair = mx_use_pair();
+    const bool pair = mx_use_pair(g.offsets != nullptr);
     int rc = make_tmap_2d(&maps.a, aq, 1, g.K, a_rows, g.K, XK, XM);
     if (rc != DK_OK) return rc;
     const bool gated = MODE == MX_OUT_GATED;
@@ -297,8 +297,8 @@ int dk_moe_grouped_gemm_mxfp8(const void* xq, const void* x_atoms, const void* w
 }
 
 int dk_mx_pair_mode(int mode) {
-    if (mode != 0 && mode != 1) {
-        dk::set_last_error("argument error: mode must be 0 or 1");
+    if (mode < -1 || mode > 1) {
+        dk::set_last_error("argument error: mode must be -1 (automatic), 0 or 1");
         return DK_ERR_ARG;
     }
     dk::g_mx_pair = mode;

@@ -450,10 +450,11 @@ mx_gemm_kernel(const __grid_constant__ MxMaps maps, const MxArgs g) {
                     // The scale columns are rewritten in place: tcgen05.cp and tcgen05.mma of one
                     // thread execute in issue order, so the copies wait for the previous MMAs and
                     // these MMAs for the copies. The copies occupy the tensor pipe: three per K
-                    // block measured 10 % of the kernel. Tried and measured no better or worse:
-                    // separate scale columns per stage, a thread of their own for the copies, and
-                    // copies issued one K block ahead of their MMAs (2.6 -> 2.3 PFLOP/s: the issuer
-                    // then has to see the NEXT stage landed before it may multiply this one).
+                    // block measured 10-20 % of the kernel depending on the board. Tried and
+                    // measured no better or worse: separate scale columns per stage, a thread of
+                    // their own for the copies, copies issued one K block ahead of their MMAs into a
+                    // second set of columns, whether waiting for the next stage (2.6 -> 2.3 PFLOP/s)
+                    // or only when it has already landed (2.38 -> 2.20).
                     if (!BLK || (kb & 3) == 0) {
                         tmem_cp_32x128b_warpx4<PAIR>(sfa_t, umma_desc_sf_atom(sf));
                         tmem_cp_32x128b_warpx4<PAIR>(sfb_t, umma_desc_sf_atom(sf + X_ATOM));

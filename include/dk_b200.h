@@ -366,10 +366,11 @@ int dk_gemm_mxfp8(const void* aq, const void* sfa, const void* bq, const void* s
  * scale, out_e8 [R/128, N/128] and out_atoms [R/128][ceil(N/512)][512]; gated = 0 writes bf16 [R, N].
  */
 /*
- * Mode 1 (DK_MX_PAIR=1 in the environment) runs dk_gemm_mxfp8 and dk_moe_grouped_gemm_mxfp8 with
- * clusters of two CTAs per 256-row tile (tcgen05 cta_group::2: half the shared-memory fill per flop,
- * a six-stage ring); mode 0 (the default: it measured as fast on large GEMMs and faster on many
- * small experts) with one CTA per 128-row tile. Results are identical. No reference counterpart.
+ * Which form of the block-scaled kernel runs: 1 = clusters of two CTAs per 256-row tile (tcgen05
+ * cta_group::2: half the shared-memory fill per flop, a six-stage ring), 0 = one CTA per 128-row
+ * tile, -1 (the default) = pairs for dk_gemm_mxfp8 and one CTA for dk_moe_grouped_gemm_mxfp8 (many
+ * small experts leave half a pair idle). DK_MX_PAIR=0/1 in the environment does the same. Results
+ * are identical. No reference counterpart.
  */
 int dk_mx_pair_mode(int mode);
 int dk_quant_block128_pow2(const void* x, int R, int C, const int* row_map, int map_mode, int k, void* q,
