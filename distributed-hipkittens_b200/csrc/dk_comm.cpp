@@ -30,6 +30,7 @@
 
 namespace dk {
 void set_last_error(const std::string& s);
+void log_msg(int level, const std::string& s);
 }
 
 struct dk_comm {
@@ -292,10 +293,12 @@ int dk_comm_create(int rank, int world, const char* rendezvous, int timeout_ms, 
                 if (!recv_all(s, &h, sizeof(h), 1000) || h.magic != HELLO_MAGIC || h.token != token || h.rank <= 0 ||
                     h.rank >= world || c->peers[h.rank] != -1) {
                     close(s);
+                    dk::log_msg(2, "rendezvous '" + name + "': a connection without a valid hello was dropped");
                     continue;
                 }
                 c->peers[h.rank] = s;
                 ++got;
+                dk::log_msg(2, "rendezvous '" + name + "': rank " + std::to_string(h.rank) + " joined");
             }
             pending.swap(still);
             if (pf[0].revents & POLLIN) {

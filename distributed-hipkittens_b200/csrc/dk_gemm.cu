@@ -1012,6 +1012,8 @@ extern "C" int dk_ag_gemm_workspace_get(const dk_view* view, int M, int K, void*
     if (rc != DK_OK) return rc;
     std::lock_guard<std::mutex> lk(h->mu);
     h->ag_ws[{M, K}] = ws;
+    dk::log_msg(1, "rank " + std::to_string(view->rank) + ": all-gather workspace for M=" + std::to_string(M) +
+                       " K=" + std::to_string(K) + ", " + std::to_string(bytes >> 20) + " MiB of the heap");
     *out = ws;
     return DK_OK;
 }
@@ -1079,6 +1081,8 @@ extern "C" int dk_gemm_rs_workspace_get(const dk_view* view, int M, int N, void*
     if (rc != DK_OK) return rc;
     std::lock_guard<std::mutex> lk(h->mu);
     h->rs_ws[{M, N}] = ws;
+    dk::log_msg(1, "rank " + std::to_string(view->rank) + ": reduce-scatter workspace for M=" + std::to_string(M) +
+                       " N=" + std::to_string(N) + ", " + std::to_string(bytes >> 20) + " MiB of the heap");
     *out = ws;
     return DK_OK;
 }

@@ -17,6 +17,7 @@
 #include <fcntl.h>
 #include <unistd.h>
 
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <vector>
@@ -278,6 +279,11 @@ int dk_heap_create(size_t bytes, int rank, int world, const char* rendezvous, dk
             return bail(DK_ERR_CUDA, "cuMemMap(rank " + std::to_string(r) + ")", cr);
         }
         h->mapped[r] = true;
+        if (log_level() >= 2) {
+            char line[96];
+            snprintf(line, sizeof line, "rank %d: heap of rank %d mapped at %#llx", rank, r, (unsigned long long)at);
+            log_msg(2, line);
+        }
         cr = api->cuMemSetAccess(at, h->bytes, &acc, 1);
         if (cr != CUDA_SUCCESS) {
             close_fds();
@@ -300,11 +306,15 @@ int dk_heap_create(size_t bytes, int rank, int world, const char* rendezvous, dk
         if (rc != DK_OK) return bail(rc, "", CUDA_SUCCESS);
     }
     *out = h;
+    log_msg(1, "rank " + std::to_string(rank) + " of " + std::to_string(world) + ": symmetric heap of " +
+                   std::to_string(h->bytes >> 20) + " MiB per rank on device " + std::to_string(h->device) +
+                   (h->mc_mapped ? ", multicast mapped" : ""));
     return DK_OK;
 }
 
 int dk_heap_destroy(dk_heap* h) {
     if (h == nullptr) return DK_OK;
+    dk::log_msg(1, "rank " + std::to_string(h->rank) + ": symmetric heap released");
     const dk::DriverApi* api;
     int rc = dk::driver_api(&api);
     if (rc != DK_OK) return rc;
@@ -337,6 +347,7 @@ int dk_heap_enable_multicast(dk_heap* h) {
     DK_CUDA_OK(cudaSetDevice(h->device));
     multicast_setup(h, api);
     cudaSetDevice(prev);
+    log_msg(1, "rank " + std::to_string(h->rank) + (h->mc_mapped ? ": multicast mapping set up" : ": no multicast mapping"));
     if (!h->mc_mapped) {
         set_last_error("NVLink multicast mapping not available (no multicast support on some rank, or a set-up "
                        "step failed there); the heap works without it");

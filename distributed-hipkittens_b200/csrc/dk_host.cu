@@ -2,6 +2,7 @@
 // the device status record.
 #include "dk_host.h"
 
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -11,6 +12,19 @@ namespace dk {
 static thread_local std::string g_last_error;
 
 void set_last_error(const std::string& s) { g_last_error = s; }
+
+static int g_log_level = -1;
+int log_level() {
+    if (g_log_level < 0) {
+        const char* e = std::getenv("DK_LOG");
+        g_log_level = (e && *e) ? std::atoi(e) : 0;
+        if (g_log_level < 0) g_log_level = 0;
+    }
+    return g_log_level;
+}
+void log_msg(int level, const std::string& s) {
+    if (level <= log_level()) fprintf(stderr, "[dk_b200] %s\n", s.c_str());
+}
 
 static DriverApi g_api;
 static std::once_flag g_api_once;
@@ -143,6 +157,7 @@ int device_status_pending() {
         site = h[2];
         detail = h[3];
     }
+    log_msg(1, "collective refused: unread device record, code " + std::to_string(code) + " site " + std::to_string(site));
     set_last_error("an earlier kernel on this device recorded an error (code " + std::to_string(code) +
                    ", block " + std::to_string(block) + ", site " + std::to_string(site) + ", detail " +
                    std::to_string(detail) + ") that has not been read with dk_last_device_status; "
@@ -179,6 +194,12 @@ unsigned long long peer_wait_ns() {
 }  // namespace dk
 
 extern "C" {
+
+int dk_set_log_level(int level) {
+    if (level < 0 || level > 2) return DK_ERR_ARG;
+    dk::g_log_level = level;
+    return DK_OK;
+}
 
 int dk_set_peer_wait_ms(int ms) {
     if (ms < 1) return DK_ERR_ARG;

@@ -13,6 +13,13 @@ namespace dk {
 
 void set_last_error(const std::string& s);
 
+// Host-side log to stderr, "[dk_b200] ...". Level 1: life cycle (heap created / destroyed, multicast
+// mapping, workspaces taken from the heap, calls refused because of an unread device record);
+// level 2: every peer mapping and rendezvous step. Shown when level <= DK_LOG (environment, default
+// 0) or the value set with dk_set_log_level.
+int log_level();
+void log_msg(int level, const std::string& s);
+
 #define DK_CUDA_OK(expr)                                                                      \
     do {                                                                                      \
         cudaError_t _e = (expr);                                                              \

@@ -15,6 +15,7 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include <cstdlib>
 #include <memory>
 #include <stdexcept>
 #include <string>
@@ -108,6 +109,13 @@ public:
             throw_on(dk_device_set(local % ndev), "set device");
         }
         heap_ = std::make_shared<HeapHolder>();
+        // DK_HEAP_MB raises (never lowers) the heap size an unmodified script asks for: the fused
+        // kernels take their workspaces from the same heap as the script's own tensors.
+        if (const char* e = std::getenv("DK_HEAP_MB")) {
+            const long long want = std::atoll(e);
+            if (want > 0 && static_cast<size_t>(want) > heap_size_mb) heap_size_mb = static_cast<size_t>(want);
+        }
+        if (verbose_ && std::getenv("DK_LOG") == nullptr) dk_set_log_level(1);
         const size_t heap_size_bytes = heap_size_mb * 1024 * 1024;
         throw_on(dk_heap_create(heap_size_bytes, rank_, world_size_, nullptr, &heap_->h),
                  "Failed to create iris heap");

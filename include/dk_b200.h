@@ -77,6 +77,13 @@ int dk_last_device_status(unsigned out[4]);
  * returns; the context stays usable. Applies to launches made after the call.
  */
 int dk_set_peer_wait_ms(int ms);
+/*
+ * Host-side log to stderr: 0 = silent (default), 1 = life cycle (heap created / destroyed, multicast
+ * mapping, workspaces taken from the heap, collectives refused because of an unread device record),
+ * 2 = also every peer mapping. DK_LOG in the environment sets the initial level. The reference has
+ * only the `verbose` flag it hands to iris (distributed-kernels/iris_py.cpp:53,61).
+ */
+int dk_set_log_level(int level);
 
 /* ------------------------------------------------------------------ symmetric heap */
 /*

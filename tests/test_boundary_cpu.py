@@ -234,3 +234,31 @@ def test_comm_needs_a_job_name(capi, monkeypatch):
     h = C.c_void_p()
     assert capi.lib().dk_comm_create(0, 2, None, 500, C.byref(h)) == capi.ERR_BOOTSTRAP
     assert b"DK_JOB_ID" in capi.lib().dk_last_error_string()
+
+
+def test_host_log_levels(capi, capfd):
+    """DK_LOG / dk_set_log_level: silent by default, level 2 reports each rank that joins a
+    rendezvous on stderr, one "[dk_b200] ..." line each."""
+    import threading
+    L = capi.lib()
+    assert L.dk_set_log_level(3) == capi.ERR_ARG and L.dk_set_log_level(-1) == capi.ERR_ARG
+
+    def job(name):
+        def rank(r):
+            h = C.c_void_p()
+            if L.dk_comm_create(r, 2, name.encode(), 15000, C.byref(h)) == 0:
+                L.dk_comm_destroy(h)
+        ts = [threading.Thread(target=rank, args=(r,)) for r in range(2)]
+        [t.start() for t in ts]
+        [t.join(30) for t in ts]
+
+    assert L.dk_set_log_level(0) == 0
+    job(f"log0{os.getpid()}")
+    assert "[dk_b200]" not in capfd.readouterr().err
+    assert L.dk_set_log_level(2) == 0
+    try:
+        job(f"log2{os.getpid()}")
+    finally:
+        L.dk_set_log_level(0)
+    err = capfd.readouterr().err
+    assert "[dk_b200] rendezvous" in err and "rank 1 joined" in err

@@ -48,7 +48,8 @@ def _oracle(orc, x, logits, w13, w2, E, k, pow2):
 @pytest.mark.parametrize("pow2", [False, True], ids=["fp32_scales", "pow2_scales"])
 @pytest.mark.parametrize("P,T,H,F,E,k,zipf", [(1, 256, 256, 128, 4, 2, 0.0), (2, 256, 256, 128, 4, 2, 0.0),
                                               (2, 384, 256, 256, 16, 8, 1.1), (4, 512, 512, 256, 16, 4, 1.1),
-                                              (8, 1024, 256, 128, 32, 8, 1.1), (8, 512, 256, 128, 8, 2, 0.0)])
+                                              (8, 1024, 256, 128, 32, 8, 1.1), (8, 512, 256, 128, 8, 2, 0.0),
+                                              (8, 2048, 256, 128, 256, 8, 1.1)])   # 32 experts per rank, some empty
 def test_ep_layer_call_all_ranks_on_one_gpu(capi, orc, P, T, H, F, E, k, zipf, pow2):
     epr, Tl = E // P, T // P
     ws_bytes = capi.moe_ep_workspace_bytes(Tl, k, E, H, F, P)
