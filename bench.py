@@ -581,9 +581,12 @@ class Moe:
     def __init__(self, ctx, which, scales="fp32"):
         """scales: "fp32" = 128x128 blocks with fp32 scales, promoted in software every 128 of K (the
         format the configurations name); "pow2" = the same blocks with power-of-two scales, applied
-        by the tensor core (tcgen05 block-scaled MMA)."""
+        by the tensor core (tcgen05 block-scaled MMA); "pow2_fp8" = as "pow2", and every token is
+        quantised per 128 channels on its home rank and crosses NVLink as fp8 (1x128 activation scales)."""
         import torch
         self.ctx = ctx
+        self.pow2 = scales != "fp32"
+        self.mode = {"fp32": 0, "pow2": 1, "pow2_fp8": 2}[scales]
         s = self.SHAPES[which]
         self.which = which
         self.metric = which + "_tflops"
@@ -607,7 +610,7 @@ class Moe:
         w13q, w13s, w2q, w2s = [], [], [], []
 
         def quant_w(w):
-            if scales == "pow2":
+            if self.pow2:
                 q, _, _, atoms = capi.quant_block128_pow2(w)
                 return q, atoms
             return capi.quant_block128(w)
@@ -623,7 +626,7 @@ class Moe:
             del w
         self.w13q, self.w13s = torch.stack(w13q), torch.stack(w13s)
         self.w2q, self.w2s = torch.stack(w2q), torch.stack(w2s)
-        if scales == "pow2":      # block atoms of all experts, one row block after the other
+        if self.pow2:             # block atoms of all experts, one row block after the other
             self.w13s = self.w13s.reshape(-1, self.w13s.shape[-2], 512)
             self.w2s = self.w2s.reshape(-1, self.w2s.shape[-2], 512)
         del w13q, w2q
@@ -644,7 +647,7 @@ class Moe:
     def step(self, i):
         ctx = self.ctx
         return ctx.tk.moe_layer_ep(self.x, self.logits, self.s["k"], self.w13q, self.w13s, self.w2q, self.w2s,
-                                   self.out, self.ws, ctx.view, 1 if self.scales == "pow2" else 0, self.counts)
+                                   self.out, self.ws, ctx.view, self.mode, self.counts)
 
     def time_gemm(self):
         """The two grouped GEMMs timed inside the layer (events recorded by the call itself), median of
@@ -659,8 +662,7 @@ class Moe:
         for i in range(5):
             ctx.capi.moe_ep_layer(self.x, self.logits, self.w13q, self.w13s, self.w2q, self.w2s, self.out,
                                   self.ws.data_ptr(), ctx.dkview, self.s["k"],
-                                  scale_mode=1 if self.scales == "pow2" else 0, counts_out=self.counts,
-                                  gemm_events=e)
+                                  scale_mode=self.mode, counts_out=self.counts, gemm_events=e)
             ctx.barrier()
             ts.append(e[0].elapsed_time(e[1]))
         ts.sort()
@@ -704,7 +706,11 @@ class Moe:
         rop, por, offs, _ = capi.moe_permute(idx, E, 128, experts_per_segment=self.epr)
         por_me, offs_me = (por, offs) if P == 1 else (por[r].contiguous(), offs[r].contiguous())
         cap = por_me.shape[0]
-        if self.scales == "pow2":
+        if self.mode == 2:
+            q, atoms = self._rows128_pow2(x_all, por_me, k)
+            y = capi.moe_ffn_mxfp8(q, atoms, self.w13q, self.w13s, self.w2q, self.w2s, offs_me)
+            del atoms
+        elif self.pow2:
             q, _, _, atoms = capi.quant_block128_pow2(x_all, rows=cap, row_map=por_me, map_mode=1, k=k)
             y = capi.moe_ffn_mxfp8(q, atoms, self.w13q, self.w13s, self.w2q, self.w2s, offs_me)
         else:
@@ -727,10 +733,43 @@ class Moe:
         del contrib
         return ctx.max_over_ranks(err)
 
+    @staticmethod
+    def _rows128_pow2(x_all, por, k):
+        """The check's own statement of the fp8 dispatch, in torch on the GPU: expert rows gathered
+        from the tokens, every 1x128 group of a row scaled by s = 2^ceil(log2(amax/448)) (1 for
+        zeros) and rounded to e4m3; the scale bytes as the atoms the grouped GEMM reads (row slot
+        i = 32*i1 + i0 of a 128-row block owns bytes i0*16 + i1*4 .. +3 of each atom of four column
+        blocks). Returns (q uint8 [cap, H], atoms uint8 [cap/128, ceil(H/512), 512])."""
+        import torch
+        cap, H = por.shape[0], x_all.shape[1]
+        nb = H // 128
+        nj = (nb + 3) // 4
+        q = torch.zeros(cap, H, dtype=torch.uint8, device="cuda")
+        e8 = torch.full((cap, 4 * nj), 127, dtype=torch.uint8, device="cuda")
+        for r0 in range(0, cap, 8192):
+            pr = por[r0:r0 + 8192].long()
+            live = pr >= 0
+            xf = x_all[(pr.clamp(min=0) // k)].float() * live[:, None]
+            g = xf.reshape(-1, nb, 128)
+            amax = g.abs().amax(dim=2)
+            m, e = torch.frexp(amax / 448.0)
+            e = torch.where(m == 0.5, e - 1, e).to(torch.int32)
+            e = torch.where(amax > 0, e, torch.zeros_like(e)).clamp(-127, 127)
+            sc = torch.ldexp(torch.ones_like(amax), e)
+            q[r0:r0 + 8192] = (g / sc[:, :, None]).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).reshape(-1, H).view(torch.uint8)
+            e8[r0:r0 + 8192, :nb] = (e + 127).to(torch.uint8)
+        atoms = e8.reshape(cap // 128, 4, 32, nj, 4).permute(0, 3, 2, 1, 4).contiguous().reshape(cap // 128, nj, 512)
+        return q, atoms
+
     def exchange_volume(self):
-        """NVLink bytes this rank's tokens cause (after check() has counted them): dispatch sends and
-        combine returns one bf16 vector per (token, other GPU)."""
+        """NVLink bytes this rank's tokens cause (after check() has counted them): dispatch sends one
+        vector per (token, other GPU), bf16 or (fp8 dispatch) e4m3 + one scale byte per 128 channels
+        padded to 16 bytes; combine returns one bf16 vector per (token, other GPU)."""
         vb = self.s["H"] * 2
+        if self.mode == 2:
+            return {"dispatch_egress_bytes_rank0": self._vectors * (self.s["H"] + (self.s["H"] // 128 + 15) // 16 * 16),
+                    "combine_ingress_bytes_rank0": self._vectors * vb,
+                    "vectors_per_direction_rank0": self._vectors, "pairs_on_other_gpus_rank0": self._remote_pairs}
         return {"dispatch_egress_bytes_rank0": self._vectors * vb, "combine_ingress_bytes_rank0": self._vectors * vb,
                 "vectors_per_direction_rank0": self._vectors, "pairs_on_other_gpus_rank0": self._remote_pairs}
 
@@ -752,7 +791,8 @@ class Moe:
     def config(self, value):
         s, P = self.s, self.ctx.world
         c = {"workload": f"fp8 MoE layer, {s['name']}, 128x128 block scales "
-                         f"({'power-of-two, applied by the tensor core' if self.scales == 'pow2' else 'fp32, promoted in software'}), EP={P}",
+                         f"({'power-of-two, applied by the tensor core' if self.pow2 else 'fp32, promoted in software'})"
+                         f"{', tokens dispatched as fp8 with 1x128 scales' if self.mode == 2 else ''}, EP={P}",
              "l2": f"expert weights ({(self.w13q.numel() + self.w2q.numel()) / 1e6:.0f} MB fp8 on this GPU) exceed L2",
              "per_gpu_tflops": value / P}
         if self.gemm_ms:
@@ -775,7 +815,7 @@ class Moe:
         return {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
                 "frac": ach / peak if peak else None,
                 "frac_of_nominal_4500": ach / 4500.0,
-                "traffic": load_traffic(self.metric + ("_pow2" if self.scales == "pow2" else "")), "of": what,
+                "traffic": load_traffic(self.metric + ("_pow2" if self.pow2 else "")), "of": what,
                 "peak_source": f"2 x {peak_src} cuBLAS bf16 ({'sustained' if sustained else 'burst'}) "
                                f"taken as the fp8 dense peak"}
 
@@ -873,7 +913,7 @@ def moe_secondary(ctx, which, scales, peaks, tokens=0):
          "roofline_frac_of_nominal_4500": gemm_tf / 4500.0,
          "non_gemm_share_of_step": max(0.0, 1.0 - wl.gemm_ms_max / ms),
          "pairs_rank0": wl.pairs_rank, "pairs_max_rank": wl.pairs_max,
-         "traffic": load_traffic(wl.metric + ("_pow2" if scales == "pow2" else "")),
+         "traffic": load_traffic(wl.metric + ("_pow2" if scales != "fp32" else "")),
          "check_rel_fro": err}
     e.update(wl.exchange_volume())
     assert err <= 2e-2, f"{which} ({scales}): layer differs from the NCCL-exchanged reference by {err}"
@@ -1018,7 +1058,8 @@ def run_emulated(args, out):
         T, H, F, k = args.tokens or 4096, sh["H"], sh["F"], sh["k"]
         E = args.experts or sh["E"]
         epr, Tl = E // P, T // P
-        pow2 = args.scales == "pow2"
+        pow2 = args.scales != "fp32"
+        mode = {"fp32": 0, "pow2": 1, "pow2_fp8": 2}[args.scales]
         buf, views, ws = job(capi.moe_ep_workspace_bytes(Tl, k, E, H, F, P))
         ranks = []
         for r in range(P):
@@ -1040,7 +1081,7 @@ def run_emulated(args, out):
             for ph in (1, 2, 4, 8):
                 for r, d in enumerate(ranks):
                     capi.moe_ep_layer(d["x"], d["logits"], d["w13q"], d["w13s"], d["w2q"], d["w2s"], d["out"], ws[r],
-                                      views[r], k, scale_mode=1 if pow2 else 0, epoch=seq, phases=ph)
+                                      views[r], k, scale_mode=mode, epoch=seq, phases=ph)
         ms, _ = timed(layer)
         res.update({"layer_ms_all_ranks": ms, "tokens": T, "experts": E, "H": H, "F": F, "k": k, "scales": args.scales})
     st = capi.device_status()
@@ -1058,9 +1099,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gemm_rs",
                     choices=["gemm_rs", "ag_gemm", "gemm_mxfp8", "allreduce", "moe_mixtral", "moe_dsv3"])
-    ap.add_argument("--scales", default="fp32", choices=["fp32", "pow2"],
+    ap.add_argument("--scales", default="fp32", choices=["fp32", "pow2", "pow2_fp8"],
                     help="MoE workloads: fp32 128x128 block scales (software promotion) or power-of-two "
-                         "block scales applied by the block-scaled MMA")
+                         "block scales applied by the block-scaled MMA; pow2_fp8: the latter with every token "
+                         "quantised per 128 channels at home and dispatched as fp8")
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
@@ -1237,7 +1279,7 @@ def main():
         if world > 1:
             sec["allreduce"] = allreduce_secondary(ctx)
         for which in ("moe_mixtral", "moe_dsv3"):
-            for scales in ("fp32", "pow2"):
+            for scales in ("fp32", "pow2", "pow2_fp8"):
                 sec[f"{which}_{scales}"] = moe_secondary(ctx, which, scales, peaks)
         if world == 1:
             sys.path.insert(0, str(ROOT / "examples"))

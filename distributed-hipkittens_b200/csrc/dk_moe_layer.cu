@@ -17,8 +17,16 @@
 //   tokbuf           [T, H] bf16   on rank d: row slot[d][t] = hidden vector of token t
 //   rows             per rank the usual permuted, 128-padded expert rows; the quantiser gathers row r
 //                    from tokbuf[slot[me][pair_of_row[r] / k]]
+//                    With scale_mode 2 the tokens cross as fp8: the source quantises every token per 128
+//                    channels with a power-of-two scale (1x128 scales, one e8m0 byte each) and sends
+//                    H + H/128 bytes instead of 2H; tokbuf then holds [T, H] e4m3 followed by
+//                    [T, sb] scale bytes (sb = H/128 rounded up to 16), and the receiving side only
+//                    gathers bytes into expert order and lays the rows' scale bytes out as the atoms
+//                    the block-scaled tensor-core path reads (they are per row by construction).
 //   partial[d]       [T_loc, H] bf16 on the home rank: sum over the token's experts on rank d of
 //                    w * y, formed in fp32 on rank d; the home rank adds the partials in rank order
+#include <cuda_fp8.h>
+
 #include "dk_moe_int.h"
 
 namespace dk {
@@ -175,6 +183,132 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(const EpDispatchArgs a
     ep_signal_done(a.sig);
 }
 
+// ---- dispatch as fp8 (scale_mode 2): the token is quantised here, once, per 128 channels with a
+// power-of-two scale (the rule of the 128x128 quantiser applied to a 1x128 group: s =
+// 2^ceil(log2(amax/448)), 1 for zeros), and its H e4m3 bytes + H/128 scale bytes go to each rank that
+// holds one of its experts. Thread c owns 16 channels; eight neighbouring lanes own one group.
+struct EpDispatchQArgs {
+    const uint4* x;                  // [T_loc, H/8] local tokens (bf16)
+    const int* slot;                 // [P][T]
+    uint8_t* tokq[DK_MAX_RANKS];     // [T, H] e4m3 at rank d
+    uint8_t* toks[DK_MAX_RANKS];     // [T, sb] e8m0 at rank d
+    int T, T_loc, H, sb, world, rank;
+    EpSignal sig;
+};
+constexpr int EP_MAX_SB = 256;  // scale bytes per token the kernels hold in shared memory (H <= 32768)
+
+__global__ void __launch_bounds__(256) ep_dispatch_q_kernel(const EpDispatchQArgs a) {
+    __shared__ int slot_s[DK_MAX_RANKS];
+    __shared__ __align__(16) uint8_t sc_s[EP_MAX_SB];
+    const int nvec = a.H / 16;
+    for (int tl = blockIdx.x; tl < a.T_loc; tl += gridDim.x) {
+        const int t = a.rank * a.T_loc + tl;
+        __syncthreads();  // the previous token's slots and scale bytes have been used
+        if (threadIdx.x < a.world) slot_s[threadIdx.x] = a.slot[static_cast<size_t>(threadIdx.x) * a.T + t];
+        for (int i = threadIdx.x; i < a.sb; i += blockDim.x) sc_s[i] = 127;  // bytes past H/128: scale 1
+        __syncthreads();
+        for (int c0 = 0; c0 < nvec; c0 += blockDim.x) {  // uniform trip count: the shuffles need whole warps
+            const int c = c0 + threadIdx.x;
+            const bool live = c < nvec;
+            uint4 u[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+            if (live) {
+                u[0] = a.x[static_cast<size_t>(tl) * (a.H / 8) + 2 * c];
+                u[1] = a.x[static_cast<size_t>(tl) * (a.H / 8) + 2 * c + 1];
+            }
+            __nv_bfloat162 m2 = __float2bfloat162_rn(0.f);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u[i]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) m2 = __hmax2(m2, __habs2(h[j]));
+            }
+            float amax = fmaxf(__low2float(m2), __high2float(m2));
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            int ex = 0;
+            if (amax > 0.f) {
+                const float m = frexpf(amax / 448.0f, &ex);
+                if (m == 0.5f) ex -= 1;
+                ex = max(-127, min(127, ex));
+            }
+            const float inv = ldexpf(1.0f, -ex);
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u[i]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __bfloat1622float2(h[j]);
+                    const uint32_t p2 = __nv_cvt_float2_to_fp8x2(make_float2(f.x * inv, f.y * inv), __NV_SATFINITE, __NV_E4M3);
+                    if (j & 1) w[2 * i + (j >> 1)] |= p2 << 16;
+                    else w[2 * i + (j >> 1)] = p2;
+                }
+            }
+            if (live) {
+                const uint4 qv = make_uint4(w[0], w[1], w[2], w[3]);
+#pragma unroll
+                for (int d = 0; d < DK_MAX_RANKS; ++d)
+                    if (d < a.world && slot_s[d] >= 0)
+                        *reinterpret_cast<uint4*>(a.tokq[d] + static_cast<size_t>(slot_s[d]) * a.H + static_cast<size_t>(c) * 16) = qv;
+                if ((threadIdx.x & 7) == 0) sc_s[c >> 3] = static_cast<uint8_t>(ex + 127);
+            }
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < a.sb / 16; i += blockDim.x) {
+            const uint4 v = reinterpret_cast<const uint4*>(sc_s)[i];
+#pragma unroll
+            for (int d = 0; d < DK_MAX_RANKS; ++d)
+                if (d < a.world && slot_s[d] >= 0)
+                    *reinterpret_cast<uint4*>(a.toks[d] + static_cast<size_t>(slot_s[d]) * a.sb + i * 16) = v;
+        }
+    }
+    ep_signal_done(a.sig);
+}
+
+// ---- the receiving side of the fp8 dispatch: expert row r takes the bytes of the token it belongs to
+// (zeros for padding rows), and the row's scale bytes go into the scale atoms of its 128-row block:
+// per four column blocks one 512-byte atom, in which row slot i = 32*i1 + i0 owns the four bytes at
+// i0*16 + i1*4 (the order in which the tensor core's scale copy spreads an atom over its 128 lanes).
+// One warp per row.
+struct EpGatherQArgs {
+    const uint8_t* tokq;             // [T, H]
+    const uint8_t* toks;             // [T, sb]
+    const int* por;                  // [cap] pair of every row, -1 = padding
+    const int* slot;                 // [T] slot of every token on this rank
+    const int* row_limit;            // rows at or beyond *row_limit are not produced
+    uint8_t* xq;                     // [cap, H]
+    uint8_t* atoms;                  // [cap/128][ceil(H/512)][512]
+    int cap, H, sb, k;
+    EpWait wait;
+};
+__global__ void __launch_bounds__(256) ep_gather_q_kernel(const EpGatherQArgs a) {
+    const int row0 = blockIdx.x * 8;
+    if (row0 >= *a.row_limit) return;
+    if (!ep_wait_sources(a.wait)) return;
+    const int r = row0 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (r >= a.cap) return;
+    const int pair = a.por[r];
+    const int src = pair >= 0 ? a.slot[pair / a.k] : -1;
+    const int nvec = a.H / 16;
+    const uint4* from = reinterpret_cast<const uint4*>(a.tokq + static_cast<size_t>(src < 0 ? 0 : src) * a.H);
+    uint4* to = reinterpret_cast<uint4*>(a.xq + static_cast<size_t>(r) * a.H);
+    for (int c = lane; c < nvec; c += 32 * 4) {  // four loads in flight per lane
+        uint4 v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            v[i] = (src >= 0 && c + 32 * i < nvec) ? __ldcg(from + c + 32 * i) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            if (c + 32 * i < nvec) to[c + 32 * i] = v[i];
+    }
+    const int nj = (a.H / 128 + 3) / 4;
+    const int i = r & 127;
+    uint8_t* atom_row = a.atoms + static_cast<size_t>(r >> 7) * nj * 512 + (i & 31) * 16 + (i >> 5) * 4;
+    const uint32_t* sc = reinterpret_cast<const uint32_t*>(a.toks + static_cast<size_t>(src < 0 ? 0 : src) * a.sb);
+    for (int j = lane; j < nj; j += 32)
+        *reinterpret_cast<uint32_t*>(atom_row + static_cast<size_t>(j) * 512) = src >= 0 ? __ldcg(sc + j) : 0x7f7f7f7fu;
+}
+
 // ---- expert-side combine: for every token that arrived here, the weighted sum of the outputs of its
 // experts on THIS rank, in fp32, pushed as one bf16 vector to the token's home rank.
 struct EpCombineArgs {
@@ -327,7 +461,9 @@ int dk_moe_ep_layer(const dk_moe_ep_args* a, const dk_view* view, unsigned epoch
     DK_REQUIRE(a->E >= 1 && a->E <= 256 && a->E % world == 0 && a->k <= a->E, "E must be 1..256, a multiple of world, >= k");
     DK_REQUIRE(a->H > 0 && a->H % 256 == 0 && a->F > 0 && a->F % 128 == 0,
                "H must be a multiple of 256 and F a multiple of 128");
-    DK_REQUIRE(a->scale_mode == 0 || a->scale_mode == 1, "scale_mode must be 0 (fp32 scales) or 1 (power-of-two)");
+    DK_REQUIRE(a->scale_mode >= 0 && a->scale_mode <= 2,
+               "scale_mode must be 0 (fp32 scales), 1 (power-of-two) or 2 (power-of-two, tokens dispatched as fp8)");
+    DK_REQUIRE(a->scale_mode != 2 || a->H / 128 <= EP_MAX_SB, "H too large for the fp8 dispatch");
     DK_REQUIRE(phases >= 1 && phases <= 15, "phases is a mask of 1 | 2 | 4 | 8");
     DK_REQUIRE(a->x && a->logits && a->w13q && a->w13s && a->w2q && a->w2s && a->out && a->workspace, "null buffer");
     DK_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 255) == 0, "the workspace must be 256-byte aligned");
@@ -347,6 +483,7 @@ int dk_moe_ep_layer(const dk_moe_ep_args* a, const dk_view* view, unsigned epoch
         return world > 1 ? static_cast<char*>(peer_ptr(view, ws + off, r)) : ws + off;
     };
     const int T = L.T, k = a->k, E = a->E, H = a->H, F = a->F, epr = L.epr, cap = L.cap;
+    const int sb = (H / 128 + 15) / 16 * 16;  // scale bytes per token of the fp8 dispatch
     int* all_idx = reinterpret_cast<int*>(at(L.all_idx));
     float* all_w = reinterpret_cast<float*>(at(L.all_w));
     int* rop = reinterpret_cast<int*>(at(L.rop));
@@ -403,7 +540,25 @@ int dk_moe_ep_layer(const dk_moe_ep_args* a, const dk_view* view, unsigned epoch
         d.rank = rank;
         d.sig = make_signal(view, EP_PH_DISPATCH, epoch);
         const int grid = a->T_loc < 4 * sms ? a->T_loc : 4 * sms;
-        if (world > 1) {
+        if (a->scale_mode == 2) {
+            // quantise at the source, send fp8 (one rank: the same kernel fills the local buffer)
+            EpDispatchQArgs dq{};
+            dq.x = d.x;
+            dq.slot = slot;
+            for (int r = 0; r < world; ++r) {
+                dq.tokq[r] = reinterpret_cast<uint8_t*>(peer(L.tokbuf, r));
+                dq.toks[r] = dq.tokq[r] + static_cast<size_t>(T) * H;
+            }
+            dq.T = T;
+            dq.T_loc = a->T_loc;
+            dq.H = H;
+            dq.sb = sb;
+            dq.world = world;
+            dq.rank = rank;
+            dq.sig = d.sig;
+            ep_dispatch_q_kernel<<<grid, 256, 0, st>>>(dq);
+            DK_CUDA_OK(cudaGetLastError());
+        } else if (world > 1) {
             ep_dispatch_kernel<<<grid, 256, 0, st>>>(d);
             DK_CUDA_OK(cudaGetLastError());
         }
@@ -417,13 +572,30 @@ int dk_moe_ep_layer(const dk_moe_ep_args* a, const dk_view* view, unsigned epoch
         if (rc != DK_OK) return rc;
         // rows of this rank's experts, gathered from the token buffer and quantised; only the rows
         // that exist (offsets[E/P], read on the device) are produced
-        const bool pow2 = a->scale_mode == 1;
-        rc = quant_block128_launch(world > 1 ? at(L.tokbuf) : a->x, cap, H, por + static_cast<size_t>(rank) * cap,
-                                   world > 1 ? 3 : 1, k, slot + static_cast<size_t>(rank) * T, my_offsets + epr,
-                                   at(L.xq),
-                                   pow2 ? nullptr : reinterpret_cast<float*>(at(L.xs)), nullptr,
-                                   pow2 ? at(L.xs) : nullptr, pow2, w, st);
-        if (rc != DK_OK) return rc;
+        const bool pow2 = a->scale_mode != 0;
+        if (a->scale_mode == 2) {
+            EpGatherQArgs g{};
+            g.tokq = reinterpret_cast<const uint8_t*>(at(L.tokbuf));
+            g.toks = g.tokq + static_cast<size_t>(T) * H;
+            g.por = por + static_cast<size_t>(rank) * cap;
+            g.slot = slot + static_cast<size_t>(rank) * T;
+            g.row_limit = my_offsets + epr;
+            g.xq = reinterpret_cast<uint8_t*>(at(L.xq));
+            g.atoms = reinterpret_cast<uint8_t*>(at(L.xs));
+            g.cap = cap;
+            g.H = H;
+            g.sb = sb;
+            g.k = k;
+            g.wait = w;
+            ep_gather_q_kernel<<<(cap + 7) / 8, 256, 0, st>>>(g);
+            DK_CUDA_OK(cudaGetLastError());
+        } else {
+            rc = quant_block128_launch(world > 1 ? at(L.tokbuf) : a->x, cap, H, por + static_cast<size_t>(rank) * cap,
+                                       world > 1 ? 3 : 1, k, slot + static_cast<size_t>(rank) * T, my_offsets + epr,
+                                       at(L.xq), pow2 ? nullptr : reinterpret_cast<float*>(at(L.xs)), nullptr,
+                                       pow2 ? at(L.xs) : nullptr, pow2, w, st);
+            if (rc != DK_OK) return rc;
+        }
         if (a->ev_gemm_begin != nullptr) DK_CUDA_OK(cudaEventRecord(static_cast<cudaEvent_t>(a->ev_gemm_begin), st));
         if (pow2) {
             rc = dk_moe_grouped_gemm_mxfp8(at(L.xq), at(L.xs), a->w13q, a->w13s, my_offsets, epr, cap, F, H, 1,

@@ -366,8 +366,8 @@ py::object moe_layer_ep(py::object X, py::object logits, int k, py::object W13q,
                         py::object counts) {
     TensorArg x = tensor_arg(X, "torch.bfloat16"), lg = tensor_arg(logits, "torch.float32");
     TensorArg w13q = tensor_arg(W13q, "torch.uint8"), w2q = tensor_arg(W2q, "torch.uint8");
-    TensorArg w13s = tensor_arg(W13s, scale_mode == 1 ? "torch.uint8" : "torch.float32");
-    TensorArg w2s = tensor_arg(W2s, scale_mode == 1 ? "torch.uint8" : "torch.float32");
+    TensorArg w13s = tensor_arg(W13s, scale_mode != 0 ? "torch.uint8" : "torch.float32");
+    TensorArg w2s = tensor_arg(W2s, scale_mode != 0 ? "torch.uint8" : "torch.float32");
     TensorArg out = tensor_arg(Out, "torch.bfloat16"), ws = tensor_arg(Workspace, "torch.uint8");
     if (x.shape.size() != 2 || lg.shape.size() != 2 || w13q.shape.size() != 3 || w2q.shape.size() != 3)
         throw std::runtime_error("expected X [T_loc,H], logits [T_loc,E], W13q [E/P,2F,H], W2q [E/P,H,F]");
@@ -450,7 +450,8 @@ PYBIND11_MODULE(tk_kernel, m) {
           py::arg("scale_mode") = 0, py::arg("counts") = py::none(),
           "One fp8 MoE layer, expert-parallel over the ranks of the view, in one call: route, exchange, "
           "dispatch (once per token and GPU), quantise, gate/up + SiLU*mul, down, combine. "
-          "scale_mode 0: fp32 block scales; 1: power-of-two block scales on the block-scaled MMA");
+          "scale_mode 0: fp32 block scales; 1: power-of-two block scales on the block-scaled MMA; "
+          "2: as 1, tokens quantised per 128 channels at home and dispatched as fp8");
     m.def("device_status", &device_status,
           "(code, block, site, detail) of the first device-side wait that gave up; clears it");
 }

@@ -435,7 +435,11 @@ int dk_moe_combine_ep(const void* y, const int* topk_idx, const int* row_of_pair
  * scale_mode 0: 128x128 blocks with fp32 scales (w13s [E/P, 2F/128, H/128], w2s [E/P, H/128, F/128]
  * fp32; dk_moe_grouped_gemm_fp8). scale_mode 1: the same blocks with power-of-two scales applied by
  * the tensor core (w13s, w2s are block atoms as dk_quant_block128_pow2 writes them;
- * dk_moe_grouped_gemm_mxfp8). H % 256 == 0, F % 128 == 0, E <= 256, k <= 8.
+ * dk_moe_grouped_gemm_mxfp8). scale_mode 2: weights as in mode 1; every token is quantised on its
+ * home rank per 128 channels with a power-of-two scale (1x128 activation scales) and crosses NVLink
+ * as H e4m3 bytes + H/128 scale bytes instead of 2H bytes of bf16; the receiving rank only gathers
+ * bytes into expert order (the per-row scales are what the tensor core's scale atoms hold anyway).
+ * H % 256 == 0, F % 128 == 0, E <= 256, k <= 8.
  *
  * workspace: dk_moe_ep_workspace_bytes(...) bytes, 256-byte aligned; for world > 1 inside the
  * symmetric heap at the same offset on every rank. Its contents need no initialisation. Calls on

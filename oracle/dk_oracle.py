@@ -237,6 +237,43 @@ def block128_scales_to_block_atoms(e8m0: torch.Tensor) -> torch.Tensor:
     return pad.reshape(Rb, j, 1, 4).expand(-1, -1, 128, -1).contiguous()
 
 
+def quant_rows128_pow2(x: torch.Tensor):
+    """Per-token quantiser of the fp8 dispatch: the power-of-two rule of quant_block128_pow2 applied
+    to every 1x128 group of a row (s = 2^ceil(log2(amax/448)), 1 for an all-zero group). Any number
+    of rows. Returns (q uint8 [R,C], s fp32 [R, C/128], e8m0 uint8 [R, C/128]).
+    A definition of this build (the reference quantises nothing on the way between GPUs)."""
+    R, Cc = x.shape
+    assert Cc % BLOCK == 0
+    xf = x.float().reshape(R, Cc // BLOCK, BLOCK)
+    amax = xf.abs().amax(dim=2)
+    m, e = torch.frexp(amax / FP8_MAX)
+    e = torch.where(m == 0.5, e - 1, e).to(torch.int32)
+    e = torch.where(amax > 0, e, torch.zeros_like(e)).clamp(-127, 127)
+    s = torch.ldexp(torch.ones_like(amax), e)
+    q = (xf / s[:, :, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return q.reshape(R, Cc).view(torch.uint8), s.contiguous(), (e + 127).to(torch.uint8)
+
+
+def dequant_rows128(q_u8: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
+    R, Cc = q_u8.shape
+    qf = q_u8.view(torch.float8_e4m3fn).float().reshape(R, Cc // BLOCK, BLOCK)
+    return (qf * s[:, :, None]).reshape(R, Cc)
+
+
+def rows128_scales_to_block_atoms(e8m0: torch.Tensor) -> torch.Tensor:
+    """1x128 power-of-two row scales [R, C/128] (R a multiple of 128) in the atoms the grouped GEMM
+    reads: [R/128, ceil(C/512), 512] bytes; inside an atom row slot i = 32*i1 + i0 of the 128-row
+    block owns the four bytes at i0*16 + i1*4, byte g = the scale of column block 4j + g (127 where
+    that block does not exist)."""
+    R, Cb = e8m0.shape
+    assert R % BLOCK == 0
+    j = (Cb + 3) // 4
+    pad = torch.full((R, 4 * j), 127, dtype=torch.uint8)
+    pad[:, :Cb] = e8m0
+    # [rb, i1, i0, j, g] -> [rb, j, i0, i1, g]
+    return pad.reshape(R // BLOCK, 4, 32, j, 4).permute(0, 3, 2, 1, 4).contiguous().reshape(R // BLOCK, j, 512)
+
+
 def dequant_block128(q_u8: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
     R, Cc = q_u8.shape
     qf = q_u8.view(torch.float8_e4m3fn).float().reshape(R // BLOCK, BLOCK, Cc // BLOCK, BLOCK)
@@ -280,6 +317,22 @@ def moe_ffn_pow2_ref(xq, xs, w13q, w13s, w2q, w2s, offsets):
     are powers of two as well; the arithmetic is the same block dequantisation).
     Returns (Y fp32 [R,H], hq u8 [R,F], hs fp32, h_e8 u8)."""
     gu = grouped_gemm_ref(xq, xs, w13q, w13s, offsets)
+    h = silu_mul(gu)
+    hq, hs, he = quant_block128_pow2(h)
+    y = grouped_gemm_ref(hq, hs, w2q, w2s, offsets)
+    return y, hq, hs, he
+
+
+def moe_ffn_rows_pow2_ref(xq, xs_rows, w13q, w13s, w2q, w2s, offsets):
+    """moe_ffn_pow2_ref for activations that arrive with 1x128 row scales (quant_rows128_pow2): the
+    gate/up GEMM dequantises every row with its own scales; from the SiLU on it is the same.
+    Returns (Y fp32 [R,H], hq u8 [R,F], hs fp32, h_e8 u8)."""
+    X = dequant_rows128(xq, xs_rows)
+    gu = torch.zeros(X.shape[0], w13q.shape[1], dtype=torch.float32)
+    for e in range(w13q.shape[0]):
+        a, b = int(offsets[e]), int(offsets[e + 1])
+        if b > a:
+            gu[a:b] = X[a:b] @ dequant_block128(w13q[e], w13s[e]).t()
     h = silu_mul(gu)
     hq, hs, he = quant_block128_pow2(h)
     y = grouped_gemm_ref(hq, hs, w2q, w2s, offsets)

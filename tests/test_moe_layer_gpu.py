@@ -5,7 +5,8 @@ waits for a later one. The multi-process form over real peer memory is in tests/
 
 Checked against the oracle's single-rank layer (the per-expert 128-row blocks hold the same rows in
 both layouts, so the quantisation is the same): per-expert pair counts bit-exact, output within 2e-2
-relative Frobenius error. Two calls in a row with different tokens on the same workspace, whose
+relative Frobenius error. With the fp8 dispatch (scale_mode 2) the oracle quantises every token per
+1x128 group before the experts see it. Two calls in a row with different tokens on the same workspace, whose
 bytes are poisoned before the first call: nothing may depend on its old contents."""
 import math
 
@@ -32,11 +33,14 @@ def _inputs(orc, T, H, F, E, k, zipf, seed, pow2):
     return x, logits.contiguous(), [st(w13, i) for i in range(len(w13[0]))], [st(w2, i) for i in range(len(w2[0]))]
 
 
-def _oracle(orc, x, logits, w13, w2, E, k, pow2):
+def _oracle(orc, x, logits, w13, w2, E, k, pow2, fp8_dispatch=False):
     idx, w = orc.moe_route(logits, k)
     rop, por, offs, counts = orc.moe_permute(idx, E)
     rows = orc.moe_gather_rows(x, por, k)
-    if pow2:
+    if fp8_dispatch:          # tokens quantised per 1x128 group where they live; rows carry their own scales
+        xq, xs, _ = orc.quant_rows128_pow2(rows)
+        y = orc.moe_ffn_rows_pow2_ref(xq, xs, w13[0], w13[1], w2[0], w2[1], offs)[0]
+    elif pow2:
         xq, xs, _ = orc.quant_block128_pow2(rows)
         y = orc.moe_ffn_pow2_ref(xq, xs, w13[0], w13[1], w2[0], w2[1], offs)[0]
     else:
@@ -45,12 +49,13 @@ def _oracle(orc, x, logits, w13, w2, E, k, pow2):
     return orc.moe_combine_ref(y, rop, w), counts
 
 
-@pytest.mark.parametrize("pow2", [False, True], ids=["fp32_scales", "pow2_scales"])
+@pytest.mark.parametrize("mode", [0, 1, 2], ids=["fp32_scales", "pow2_scales", "pow2_scales_fp8_dispatch"])
 @pytest.mark.parametrize("P,T,H,F,E,k,zipf", [(1, 256, 256, 128, 4, 2, 0.0), (2, 256, 256, 128, 4, 2, 0.0),
                                               (2, 384, 256, 256, 16, 8, 1.1), (4, 512, 512, 256, 16, 4, 1.1),
                                               (8, 1024, 256, 128, 32, 8, 1.1), (8, 512, 256, 128, 8, 2, 0.0),
                                               (8, 2048, 256, 128, 256, 8, 1.1)])   # 32 experts per rank, some empty
-def test_ep_layer_call_all_ranks_on_one_gpu(capi, orc, P, T, H, F, E, k, zipf, pow2):
+def test_ep_layer_call_all_ranks_on_one_gpu(capi, orc, P, T, H, F, E, k, zipf, mode):
+    pow2 = mode != 0
     epr, Tl = E // P, T // P
     ws_bytes = capi.moe_ep_workspace_bytes(Tl, k, E, H, F, P)
     assert ws_bytes > 0
@@ -65,7 +70,7 @@ def test_ep_layer_call_all_ranks_on_one_gpu(capi, orc, P, T, H, F, E, k, zipf, p
     capi.device_status()
     for call in (1, 2):
         x, logits, w13, w2 = _inputs(orc, T, H, F, E, k, zipf, seed=20 + call, pow2=pow2)
-        want, want_counts = _oracle(orc, x, logits, w13, w2, E, k, pow2)
+        want, want_counts = _oracle(orc, x, logits, w13, w2, E, k, pow2, fp8_dispatch=mode == 2)
         dev = []
         for r in range(P):
             es, sl = slice(r * epr, (r + 1) * epr), slice(r * Tl, (r + 1) * Tl)
@@ -82,7 +87,7 @@ def test_ep_layer_call_all_ranks_on_one_gpu(capi, orc, P, T, H, F, E, k, zipf, p
             for r in range(P):
                 d = dev[r]
                 capi.moe_ep_layer(d["x"], d["logits"], d["w13q"], d["w13s"], d["w2q"], d["w2s"], d["out"], ws[r],
-                                  views[r] if P > 1 else None, k, scale_mode=1 if pow2 else 0, epoch=call,
+                                  views[r] if P > 1 else None, k, scale_mode=mode, epoch=call,
                                   phases=phase, counts_out=d["counts"])
             torch.cuda.synchronize()
         assert capi.device_status()[0] == 0

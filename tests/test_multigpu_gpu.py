@@ -112,7 +112,8 @@ def _worker(rank, world, job, q):
         res["moe_idx_ok"] = bool(torch.equal(all_idx.cpu(), idx_c))
 
         # ---- the same layer as ONE call (dedup dispatch, expert-side combine, flags instead of
-        # barriers), fp32 scales then power-of-two scales, two calls each on one workspace
+        # barriers), fp32 scales, power-of-two scales, then the latter with the fp8 dispatch; two calls each on one
+        # workspace
         nbytes = tk_kernel.moe_ep_workspace_bytes(Tl, k, E, H, F, world)
         ws = torch.as_tensor(iris.empty([nbytes], "uint8"), device="cuda")
         ws.fill_(0xFF)                       # its contents need no initialisation
@@ -121,11 +122,15 @@ def _worker(rank, world, job, q):
         layer_errs = []
         torch.cuda.synchronize()
         iris.barrier()
-        for scale_mode in (0, 1):
+        for scale_mode in (0, 1, 2):     # 2: tokens cross as fp8 with 1x128 scales (weights as in mode 1)
             if scale_mode == 0:
                 a13, a2 = w13s[es].contiguous().cuda(), w2s[es].contiguous().cuda()
                 q13, q2 = w13q[es].contiguous().cuda(), w2q[es].contiguous().cuda()
                 want_l = want_moe
+            elif scale_mode == 2:
+                xq_r, xs_r, _ = orc.quant_rows128_pow2(orc.moe_gather_rows(x, por_c, k))
+                y_r = orc.moe_ffn_rows_pow2_ref(xq_r, xs_r, st(p13, 0), st(p13, 1), st(p2, 0), st(p2, 1), offs_c)[0]
+                want_l = orc.moe_combine_ref(y_r, rop_c, w_c)[sl]
             else:
                 import math
                 g = torch.Generator().manual_seed(99)
