@@ -8,6 +8,10 @@
 // starts with ep_wait_sources: thread r of every CTA waits (bounded) until flag [phase][r] has
 // reached the epoch, for every source rank r. The reference has nothing of the kind (it has no
 // exchange between ranks at all).
+//
+// The epoch is a host-side call number, or (epoch_ptr) one more than a word in this rank's device
+// memory that the call itself advances when all of its kernels are through: the enqueued work then
+// carries no host-side counter and can be replayed from a CUDA graph.
 #pragma once
 #include "dk_heap.h"
 #include "dk_host.h"
@@ -22,6 +26,7 @@ struct EpSignal {
     unsigned* flag[DK_MAX_RANKS];      // at rank r: flags[phase][this rank]
     int world;
     unsigned epoch;
+    const unsigned* epoch_ptr;         // not null: the call number is *epoch_ptr + 1 (device-resident)
 };
 
 struct EpWait {
@@ -30,6 +35,7 @@ struct EpWait {
     unsigned epoch;
     unsigned* status;
     unsigned long long limit_ns;
+    const unsigned* epoch_ptr;  // as in EpSignal
 };
 
 // Called by every thread of the CTA once its stores have been issued.
@@ -44,7 +50,8 @@ __device__ __forceinline__ void ep_signal_done(const EpSignal& s) {
             // ... and all counts before the flags: the last CTA publishes for the whole launch
             __threadfence_system();
             *s.counter = 0u;  // ready for the next launch on this stream
-            for (int r = 0; r < s.world; ++r) signal_store_release_sys(s.flag[r], s.epoch);
+            const unsigned epoch = s.epoch_ptr != nullptr ? *s.epoch_ptr + 1u : s.epoch;
+            for (int r = 0; r < s.world; ++r) signal_store_release_sys(s.flag[r], epoch);
         }
     }
 }
@@ -58,7 +65,8 @@ __device__ __forceinline__ bool ep_wait_sources(const EpWait& w) {
     __syncthreads();
     if (threadIdx.x < static_cast<unsigned>(w.world)) {
         const WaitCtx wc{w.status, &ep_abort, w.limit_ns};
-        signal_wait_ge(w.flags + threadIdx.x, w.epoch, wc, SITE_EP_WAIT, threadIdx.x);
+        const unsigned epoch = w.epoch_ptr != nullptr ? *w.epoch_ptr + 1u : w.epoch;
+        signal_wait_ge(w.flags + threadIdx.x, epoch, wc, SITE_EP_WAIT, threadIdx.x);
     }
     __syncthreads();
     return ep_abort == 0;

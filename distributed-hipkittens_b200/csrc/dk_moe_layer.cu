@@ -415,26 +415,38 @@ __global__ void __launch_bounds__(256) ep_final_kernel(const EpFinalArgs a) {
 // control-block words (inside DK_CTRL_MOE; the peer barrier uses words 0..7 of that region)
 constexpr size_t EP_FLAG_BASE = DK_CTRL_MOE + 64;     // flags [3 phases][8 sources]
 constexpr size_t EP_COUNTER_BASE = DK_CTRL_MOE + 128;  // CTA counters [3 phases], local use only
+// Calls whose number lives on the device (DK_EPOCH_DEVICE) have flags of their own, so that they can be
+// mixed with host-numbered calls on one heap, and the word that counts them.
+constexpr size_t EP_DEV_FLAG_BASE = DK_CTRL_MOE + 192;
+constexpr size_t EP_DEV_EPOCH = DK_CTRL_MOE + 256;
 enum : int { EP_PH_ROUTE = 0, EP_PH_DISPATCH = 1, EP_PH_COMBINE = 2 };
 
 static EpSignal make_signal(const dk_view* v, int phase, unsigned epoch) {
     EpSignal s{};
     if (v->world <= 1) return s;
+    const bool dev = epoch == DK_EPOCH_DEVICE;
+    const size_t base = dev ? EP_DEV_FLAG_BASE : EP_FLAG_BASE;
     s.counter = ctrl_words(v, v->rank) + EP_COUNTER_BASE + phase;
-    for (int r = 0; r < v->world; ++r) s.flag[r] = ctrl_words(v, r) + EP_FLAG_BASE + phase * DK_MAX_RANKS + v->rank;
+    for (int r = 0; r < v->world; ++r) s.flag[r] = ctrl_words(v, r) + base + phase * DK_MAX_RANKS + v->rank;
     s.world = v->world;
     s.epoch = epoch;
+    s.epoch_ptr = dev ? ctrl_words(v, v->rank) + EP_DEV_EPOCH : nullptr;
     return s;
 }
 static int make_wait(const dk_view* v, int phase, unsigned epoch, EpWait* w) {
     *w = EpWait{};
     if (v->world <= 1) return DK_OK;
-    w->flags = ctrl_words(v, v->rank) + EP_FLAG_BASE + phase * DK_MAX_RANKS;
+    const bool dev = epoch == DK_EPOCH_DEVICE;
+    w->flags = ctrl_words(v, v->rank) + (dev ? EP_DEV_FLAG_BASE : EP_FLAG_BASE) + phase * DK_MAX_RANKS;
     w->world = v->world;
     w->epoch = epoch;
+    w->epoch_ptr = dev ? ctrl_words(v, v->rank) + EP_DEV_EPOCH : nullptr;
     w->limit_ns = peer_wait_ns();
     return device_status_ptr(&w->status);
 }
+
+// the last launch of a device-numbered call: the next call is one later
+__global__ void ep_epoch_advance_kernel(unsigned* word) { *word += 1u; }
 
 }  // namespace dk
 
@@ -647,6 +659,10 @@ int dk_moe_ep_layer(const dk_moe_ep_args* a, const dk_view* view, unsigned epoch
         const int grid = a->T_loc < 4 * sms ? a->T_loc : 4 * sms;
         ep_final_kernel<<<grid, 256, 0, st>>>(f);
         DK_CUDA_OK(cudaGetLastError());
+        if (world > 1 && epoch == DK_EPOCH_DEVICE) {
+            ep_epoch_advance_kernel<<<1, 1, 0, st>>>(ctrl_words(view, rank) + EP_DEV_EPOCH);
+            DK_CUDA_OK(cudaGetLastError());
+        }
     }
     return DK_OK;
 }

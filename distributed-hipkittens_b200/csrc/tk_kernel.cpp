@@ -363,7 +363,7 @@ int64_t moe_ep_workspace_bytes(int T_loc, int k, int E, int H, int F, int world)
 
 py::object moe_layer_ep(py::object X, py::object logits, int k, py::object W13q, py::object W13s, py::object W2q,
                         py::object W2s, py::object Out, py::object Workspace, py::object view, int scale_mode,
-                        py::object counts) {
+                        py::object counts, bool device_epoch) {
     TensorArg x = tensor_arg(X, "torch.bfloat16"), lg = tensor_arg(logits, "torch.float32");
     TensorArg w13q = tensor_arg(W13q, "torch.uint8"), w2q = tensor_arg(W2q, "torch.uint8");
     TensorArg w13s = tensor_arg(W13s, scale_mode != 0 ? "torch.uint8" : "torch.float32");
@@ -401,7 +401,7 @@ py::object moe_layer_ep(py::object X, py::object logits, int k, py::object W13q,
         if (c.numel() * world != a.E) throw std::runtime_error("counts must hold E / world entries");
         a.counts_out = static_cast<int*>(c.ptr);
     }
-    throw_on(dk_moe_ep_layer(&a, v, 0, 15, current_stream()), "moe_layer_ep");
+    throw_on(dk_moe_ep_layer(&a, v, device_epoch ? DK_EPOCH_DEVICE : 0u, 15, current_stream()), "moe_layer_ep");
     return Out;
 }
 
@@ -447,11 +447,13 @@ PYBIND11_MODULE(tk_kernel, m) {
     m.def("moe_ep_workspace_bytes", &moe_ep_workspace_bytes, "bytes of workspace moe_layer_ep needs");
     m.def("moe_layer_ep", &moe_layer_ep, py::arg("X"), py::arg("logits"), py::arg("k"), py::arg("W13q"),
           py::arg("W13s"), py::arg("W2q"), py::arg("W2s"), py::arg("Out"), py::arg("Workspace"), py::arg("view"),
-          py::arg("scale_mode") = 0, py::arg("counts") = py::none(),
+          py::arg("scale_mode") = 0, py::arg("counts") = py::none(), py::arg("device_epoch") = false,
           "One fp8 MoE layer, expert-parallel over the ranks of the view, in one call: route, exchange, "
           "dispatch (once per token and GPU), quantise, gate/up + SiLU*mul, down, combine. "
           "scale_mode 0: fp32 block scales; 1: power-of-two block scales on the block-scaled MMA; "
-          "2: as 1, tokens quantised per 128 channels at home and dispatched as fp8");
+          "2: as 1, tokens quantised per 128 channels at home and dispatched as fp8. device_epoch: the call "
+          "number lives in device memory, so the call can be captured into a CUDA graph (after one eager call) "
+          "and replayed, every rank the same number of times");
     m.def("device_status", &device_status,
           "(code, block, site, detail) of the first device-side wait that gave up; clears it");
 }

@@ -141,13 +141,15 @@ def _(logits, k):
 @torch.library.custom_op(f"{NS}::moe_layer", mutates_args=("out", "workspace"), device_types="cuda")
 def moe_layer(x: torch.Tensor, logits: torch.Tensor, k: int, w13q: torch.Tensor, w13s: torch.Tensor,
               w2q: torch.Tensor, w2s: torch.Tensor, out: torch.Tensor, workspace: torch.Tensor, view: int,
-              scale_mode: int = 0) -> None:
-    """One expert-parallel fp8 MoE layer in one call (tk_kernel.moe_layer_ep)."""
-    _tk().moe_layer_ep(x, logits, k, w13q, w13s, w2q, w2s, out, workspace, _view(view), scale_mode, None)
+              scale_mode: int = 0, device_epoch: bool = False) -> None:
+    """One expert-parallel fp8 MoE layer in one call (tk_kernel.moe_layer_ep). device_epoch: keep the
+    call number on the device, which makes the call replayable from a CUDA graph."""
+    _tk().moe_layer_ep(x, logits, k, w13q, w13s, w2q, w2s, out, workspace, _view(view), scale_mode, None,
+                       device_epoch)
 
 
 @moe_layer.register_fake
-def _(x, logits, k, w13q, w13s, w2q, w2s, out, workspace, view, scale_mode=0):
+def _(x, logits, k, w13q, w13s, w2q, w2s, out, workspace, view, scale_mode=0, device_epoch=False):
     torch._check(x.shape == out.shape and x.shape[0] == logits.shape[0], lambda: "shapes disagree")
 
 

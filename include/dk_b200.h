@@ -447,11 +447,17 @@ int dk_moe_combine_ep(const void* y, const int* topk_idx, const int* row_of_pair
  * pairs routed to each of this rank's E / world experts.
  *
  * `epoch`: 0 takes the next epoch of the view's heap (every rank calls in the same order); views
- * without a heap handle pass the 1-based call number. `phases` selects what is enqueued: 1 routing +
+ * without a heap handle pass the 1-based call number. DK_EPOCH_DEVICE keeps the call number in device
+ * memory instead (a word of this rank's control block, advanced by the call's last launch, with flags
+ * of its own): nothing a launch is given then changes from call to call, so after one eager call the
+ * work can be captured into a CUDA graph and replayed, every rank replaying the same number of
+ * times; device-numbered and host-numbered calls can be mixed on one heap. A replay does not pass
+ * through this library, so read dk_last_device_status() after replays. `phases` selects what is enqueued: 1 routing +
  * exchange, 2 permutation + dispatch, 4 experts + combine push, 8 final sum; 15 = the layer. Running
  * all ranks of a job on one GPU means phase by phase over the ranks (no launch then waits for a
  * later one).
  */
+#define DK_EPOCH_DEVICE 0xFFFFFFFFu
 typedef struct dk_moe_ep_args {
     int T_loc, k, E, H, F;
     int scale_mode;

@@ -55,6 +55,20 @@ def _oracle(orc, x, logits, w13, w2, E, k, pow2, fp8_dispatch=False):
                                               (8, 1024, 256, 128, 32, 8, 1.1), (8, 512, 256, 128, 8, 2, 0.0),
                                               (8, 2048, 256, 128, 256, 8, 1.1)])   # 32 experts per rank, some empty
 def test_ep_layer_call_all_ranks_on_one_gpu(capi, orc, P, T, H, F, E, k, zipf, mode):
+    _run_layer(capi, orc, P, T, H, F, E, k, zipf, mode, epochs=(1, 2))
+
+
+DEVICE = 0xFFFFFFFF      # DK_EPOCH_DEVICE: the call number lives in device memory
+
+
+@pytest.mark.parametrize("mode", [0, 2], ids=["fp32_scales", "pow2_scales_fp8_dispatch"])
+def test_ep_layer_device_numbered_calls(capi, orc, mode):
+    """Calls numbered on the device (what makes the layer replayable from a CUDA graph), mixed with a
+    host-numbered call on the same heap regions: each kind has its own flags and counter."""
+    _run_layer(capi, orc, 4, 512, 256, 128, 16, 4, 1.1, mode, epochs=(DEVICE, DEVICE, 1, DEVICE))
+
+
+def _run_layer(capi, orc, P, T, H, F, E, k, zipf, mode, epochs):
     pow2 = mode != 0
     epr, Tl = E // P, T // P
     ws_bytes = capi.moe_ep_workspace_bytes(Tl, k, E, H, F, P)
@@ -68,7 +82,7 @@ def test_ep_layer_call_all_ranks_on_one_gpu(capi, orc, P, T, H, F, E, k, zipf, m
     for r in range(P):      # the workspace needs no initialisation: poison it (the flags stay zero)
         capi.tensor_from_ptr(ws[r], (ws_bytes,), torch.uint8).fill_(0xFF)
     capi.device_status()
-    for call in (1, 2):
+    for call, epoch in enumerate(epochs, 1):
         x, logits, w13, w2 = _inputs(orc, T, H, F, E, k, zipf, seed=20 + call, pow2=pow2)
         want, want_counts = _oracle(orc, x, logits, w13, w2, E, k, pow2, fp8_dispatch=mode == 2)
         dev = []
@@ -87,7 +101,7 @@ def test_ep_layer_call_all_ranks_on_one_gpu(capi, orc, P, T, H, F, E, k, zipf, m
             for r in range(P):
                 d = dev[r]
                 capi.moe_ep_layer(d["x"], d["logits"], d["w13q"], d["w13s"], d["w2q"], d["w2s"], d["out"], ws[r],
-                                  views[r] if P > 1 else None, k, scale_mode=mode, epoch=call,
+                                  views[r] if P > 1 else None, k, scale_mode=mode, epoch=epoch,
                                   phases=phase, counts_out=d["counts"])
             torch.cuda.synchronize()
         assert capi.device_status()[0] == 0
@@ -120,3 +134,41 @@ def test_ep_layer_python_entry_point_one_rank(orc):
     assert tk_kernel.device_status()[0] == 0
     assert torch.equal(counts.cpu(), want_counts)
     assert orc.rel_fro(out.float().cpu(), want) <= TOL
+
+
+@pytest.mark.parametrize("mode", [1, 2], ids=["pow2_scales", "pow2_scales_fp8_dispatch"])
+def test_ep_layer_replayed_from_a_cuda_graph(orc, mode):
+    """The whole layer (route .. final sum, 12 launches) captured once into a CUDA graph after one
+    eager call and replayed on new tokens written into the captured buffers. One rank; the ranks of
+    a real job do the same with device-numbered calls (tests/test_multigpu_gpu.py)."""
+    import tk_kernel
+    T, H, F, E, k = 512, 256, 256, 8, 2
+    nbytes = tk_kernel.moe_ep_workspace_bytes(T, k, E, H, F, 1)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    xs = torch.zeros(T, H, dtype=torch.bfloat16, device="cuda")
+    ls = torch.zeros(T, E, dtype=torch.float32, device="cuda")
+    out = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+    counts = torch.empty(E, dtype=torch.int32, device="cuda")
+    x, logits, w13, w2 = _inputs(orc, T, H, F, E, k, 1.1, seed=40, pow2=True)
+    dw = [w13[0].cuda(), orc.block128_scales_to_block_atoms(w13[2].reshape(-1, w13[2].shape[-1])).cuda(),
+          w2[0].cuda(), orc.block128_scales_to_block_atoms(w2[2].reshape(-1, w2[2].shape[-1])).cuda()]
+    call = lambda: tk_kernel.moe_layer_ep(xs, ls, k, dw[0], dw[1], dw[2], dw[3], out, ws, None, mode, counts, True)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        call()                       # eager once: everything the library sets up lazily exists afterwards
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        call()
+    for seed in (41, 42, 43):
+        x, logits, _, _ = _inputs(orc, T, H, F, E, k, 1.1, seed=seed, pow2=True)
+        want, want_counts = _oracle(orc, x, logits, w13, w2, E, k, True, fp8_dispatch=mode == 2)
+        xs.copy_(x)
+        ls.copy_(logits)
+        out.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert tk_kernel.device_status()[0] == 0
+        assert torch.equal(counts.cpu(), want_counts)
+        assert orc.rel_fro(out.float().cpu(), want) <= TOL

@@ -152,6 +152,34 @@ def _worker(rank, world, job, q):
                                        out_l, ws, view, scale_mode, counts)
                 torch.cuda.synchronize()
                 layer_errs.append(orc.rel_fro(out_l.float().cpu(), want_l))
+        # the same call with its number kept on the device, captured into a CUDA graph after one eager
+        # call and replayed on new tokens (weights and scale mode of the last round above)
+        xs_g, ls_g = x[sl].contiguous().cuda(), logits[sl].contiguous().cuda()
+        counts_g = torch.empty_like(counts)
+        call = lambda: tk_kernel.moe_layer_ep(xs_g, ls_g, k, q13, a13, q2, a2, out_l, ws, view, 2, counts_g, True)
+        call()
+        torch.cuda.synchronize()
+        iris.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            call()
+        for seed in (71, 72):
+            gg = torch.Generator().manual_seed(seed)
+            x_g = torch.randn(T, H, generator=gg).to(torch.bfloat16)
+            lg_g = torch.randn(T, E, generator=gg)
+            idx_g, w_g = orc.moe_route(lg_g, k)
+            rop_g, por_g, offs_g, _ = orc.moe_permute(idx_g, E)
+            xq_r, xs_r, _ = orc.quant_rows128_pow2(orc.moe_gather_rows(x_g, por_g, k))
+            y_r = orc.moe_ffn_rows_pow2_ref(xq_r, xs_r, st(p13, 0), st(p13, 1), st(p2, 0), st(p2, 1), offs_g)[0]
+            want_g = orc.moe_combine_ref(y_r, rop_g, w_g)[sl]
+            xs_g.copy_(x_g[sl])
+            ls_g.copy_(lg_g[sl])
+            out_l.fill_(float("nan"))
+            torch.cuda.synchronize()
+            graph.replay()
+            torch.cuda.synchronize()
+            layer_errs.append(orc.rel_fro(out_l.float().cpu(), want_g))
+        del graph
         res["moe_layer"] = layer_errs
         want_counts = torch.bincount(idx_c.reshape(-1).long(), minlength=E)[es]
         res["moe_layer_counts_ok"] = bool(torch.equal(counts.cpu().long(), want_counts))
