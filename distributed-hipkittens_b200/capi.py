@@ -127,6 +127,7 @@ def _declare(L: C.CDLL) -> None:
     L.dk_peer_barrier_epoch.argtypes = [C.POINTER(DkView), C.c_uint, vp]
     L.dk_set_peer_wait_ms.argtypes = [i]
     L.dk_set_log_level.argtypes = [i]
+    L.dk_set_walk_band_bytes.argtypes = [sz]
     L.dk_allgather.argtypes = [vp, sz, vp, C.POINTER(DkView), vp]
     L.dk_moe_dispatch.argtypes = [vp, vp, vp, i, i, i, i, vp, C.POINTER(DkView), i, vp]
     L.dk_moe_combine_ep.argtypes = [vp, vp, vp, vp, i, i, i, i, vp, C.POINTER(DkView), i, vp]

@@ -13,6 +13,17 @@ static thread_local std::string g_last_error;
 
 void set_last_error(const std::string& s) { g_last_error = s; }
 
+static long long g_band_bytes = 0;
+int walk_band_tiles(int tile_rows, int K) {
+    if (g_band_bytes == 0) {
+        const char* e = std::getenv("DK_WALK_BAND_MB");
+        const long long mb = (e && *e) ? std::atoll(e) : 32;
+        g_band_bytes = (mb > 0 ? mb : 32) << 20;
+    }
+    const long long t = g_band_bytes / (static_cast<long long>(tile_rows) * K);
+    return t < 1 ? 1 : (t > (1 << 20) ? (1 << 20) : static_cast<int>(t));
+}
+
 static int g_log_level = -1;
 int log_level() {
     if (g_log_level < 0) {
@@ -194,6 +205,12 @@ unsigned long long peer_wait_ns() {
 }  // namespace dk
 
 extern "C" {
+
+int dk_set_walk_band_bytes(size_t bytes) {
+    if (bytes == 0 || bytes > (size_t{1} << 40)) return DK_ERR_ARG;
+    dk::g_band_bytes = static_cast<long long>(bytes);
+    return DK_OK;
+}
 
 int dk_set_log_level(int level) {
     if (level < 0 || level > 2) return DK_ERR_ARG;

@@ -17,6 +17,11 @@ void set_last_error(const std::string& s);
 // mapping, workspaces taken from the heap, calls refused because of an unread device record);
 // level 2: every peer mapping and rendezvous step. Shown when level <= DK_LOG (environment, default
 // 0) or the value set with dk_set_log_level.
+// Row tiles per band of the grouped GEMMs' tile walk: as many tiles of `tile_rows` x K bytes of the
+// row operand as fit into the band size (32 MB, a quarter of L2, unless DK_WALK_BAND_MB or
+// dk_set_walk_band_bytes says otherwise). At least 1.
+int walk_band_tiles(int tile_rows, int K);
+
 int log_level();
 void log_msg(int level, const std::string& s);
 

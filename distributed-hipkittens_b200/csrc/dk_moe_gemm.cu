@@ -55,6 +55,7 @@ struct GroupedArgs {
     int R;               // rows of X and of the output
     int num_kb;          // K / 128
     int n_tiles;         // gated: F/128, plain: N/256
+    int band;            // row tiles per band of the tile walk (>= 1)
     int w_rows;          // rows of one expert's weight: gated 2F, plain N
     int w_blocks;        // w_rows / 128
     uint8_t* hq;         // gated out [R, F]
@@ -70,15 +71,25 @@ enum : unsigned { GS_EMPTY = 32, GS_FULL = 33, GS_TEMPTY = 34, GS_TFULL = 35, GS
 struct TileWalk {
     const int* cum;      // [E+1] in shared memory
     const int* offs;     // [E+1] in shared memory
-    int E, n_tiles, e;
+    int E, n_tiles, e, band;
     __device__ __forceinline__ bool locate(int t, int& expert, int& row0, int& n) {
         if (t >= cum[E]) return false;
         while (t >= cum[e + 1]) ++e;
         const int local = t - cum[e];
         const int mt = (offs[e + 1] - offs[e]) / GM;
         expert = e;
-        row0 = offs[e] + (local % mt) * GM;
-        n = local / mt;
+        int rt;
+        if (mt <= band) {
+            rt = local % mt;
+            n = local / mt;
+        } else {  // band by band: a band's rows of X stay in L2 while all column tiles pass
+            const int per_band = band * n_tiles;
+            const int b = local / per_band, rem = local - b * per_band;
+            const int in_band = min(band, mt - b * band);
+            n = rem / in_band;
+            rt = b * band + rem - n * in_band;
+        }
+        row0 = offs[e] + rt * GM;
         return true;
     }
 };
@@ -170,7 +181,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GroupedMaps maps, const GroupedA
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    TileWalk walk{cum_sm, offs_sm, g.E, g.n_tiles, 0};
+    TileWalk walk{cum_sm, offs_sm, g.E, g.n_tiles, 0, g.band};
 
     // Registers are re-balanced between the warpgroups: the promotion warps hold 128 accumulators
     // plus 64 values in flight from TMEM, far above the 168 registers a 384-thread block is
@@ -435,6 +446,8 @@ extern "C" int dk_moe_grouped_gemm_fp8(const void* xq, const float* xs, const vo
     g.R = R;
     g.num_kb = K / GK;
     g.n_tiles = gated ? N / 128 : N / GN;
+    // an expert with more rows than L2 holds is read from DRAM once, not once per column tile
+    g.band = walk_band_tiles(GM, K);
     g.w_rows = w_rows;
     g.w_blocks = w_rows / 128;
     g.hq = static_cast<uint8_t*>(out);

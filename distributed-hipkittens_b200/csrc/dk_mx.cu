@@ -162,6 +162,8 @@ template <int MODE, bool BLK>
 static int launch_mx(MxMaps& maps, MxArgs& g, const void* aq, int a_rows, const void* bq, uint64_t b_rows_total,
                      int row_tiles_upper, cudaStream_t st) {
     const bool pair = mx_use_pair(g.offsets != nullptr);
+    // rows of A that stay in L2 while all column tiles of a band pass (a quarter of L2)
+    g.band = walk_band_tiles(XM * (pair ? 2 : 1), g.K);  // dk_host.cu
     int rc = make_tmap_2d(&maps.a, aq, 1, g.K, a_rows, g.K, XK, XM);
     if (rc != DK_OK) return rc;
     const bool gated = MODE == MX_OUT_GATED;

@@ -69,6 +69,7 @@ struct MxArgs {
     int E, K, N;          // N: output columns (gated: F)
     int num_kb;           // K / 128
     int n_tiles;          // gated: F/128, plain: ceil(N/256)
+    int band;             // row tiles per band of the tile walk (>= 1)
     int w_rows;           // rows of one group's B matrix: gated 2F, plain N
     int w_blocks;         // 128-row blocks of one group's B matrix
     int sfa_blocks;       // 128-row blocks in sfa / sfb altogether (atom indices are clamped to them)
@@ -84,21 +85,34 @@ struct MxArgs {
 enum : unsigned { XS_EMPTY = 64, XS_FULL = 65, XS_TEMPTY = 66, XS_TFULL = 67, XS_EPI = 68, XS_OFFSETS = 69 };
 
 // Tile walk shared by all roles: tile t -> (group, first row of the tile, column tile, rows left in
-// the group from there). A tile covers 128 * PAIR rows. Row tiles fastest, so CTAs running together
-// share one B tile in L2. cum[e] = tiles before group e.
+// the group from there). A tile covers 128 * PAIR rows. Inside a group the tiles go band by band: a
+// band is `band` row tiles; inside a band row tiles run fastest, then column tiles. CTAs running
+// together share a B tile in L2, and a band's rows of A (sized by the host to a fraction of L2) stay
+// there while all column tiles pass, so a group with more rows than L2 holds is still read from DRAM
+// once, not once per column tile. cum[e] = tiles before group e.
 struct MxWalk {
     const int* cum;   // [E+1] in shared memory
     const int* offs;  // [E+1] in shared memory
-    int E, e, tile_rows;
+    int E, e, tile_rows, n_tiles, band;
     __device__ __forceinline__ bool locate(int t, int& group, int& row0, int& n, int& rows_left) {
         if (t >= cum[E]) return false;
         while (t >= cum[e + 1]) ++e;
         const int local = t - cum[e];
         const int mt = (offs[e + 1] - offs[e] + tile_rows - 1) / tile_rows;
         group = e;
-        row0 = offs[e] + (local % mt) * tile_rows;
+        int rt;
+        if (mt <= band) {
+            rt = local % mt;
+            n = local / mt;
+        } else {
+            const int per_band = band * n_tiles;
+            const int b = local / per_band, rem = local - b * per_band;
+            const int in_band = min(band, mt - b * band);
+            n = rem / in_band;
+            rt = b * band + rem - n * in_band;
+        }
+        row0 = offs[e] + rt * tile_rows;
         rows_left = offs[e + 1] - row0;
-        n = local / mt;
         return true;
     }
 };
@@ -351,7 +365,7 @@ mx_gemm_kernel(const __grid_constant__ MxMaps maps, const MxArgs g) {
     }
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    MxWalk walk{cum_sm, offs_sm, g.E, 0, XM * PAIR};
+    MxWalk walk{cum_sm, offs_sm, g.E, 0, XM * PAIR, g.n_tiles, g.band};
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer

@@ -84,6 +84,13 @@ int dk_set_peer_wait_ms(int ms);
  * only the `verbose` flag it hands to iris (distributed-kernels/iris_py.cpp:53,61).
  */
 int dk_set_log_level(int level);
+/*
+ * Tuning knob of the grouped and block-scaled GEMMs' tile order. Inside a group (an expert) tiles run
+ * band by band; a band is as many row tiles as hold `bytes` of the row operand, and inside a band row
+ * tiles run fastest, then column tiles: the band's rows stay in L2 while all column tiles pass.
+ * Default 32 MB (DK_WALK_BAND_MB in the environment). Results do not depend on it.
+ */
+int dk_set_walk_band_bytes(size_t bytes);
 
 /* ------------------------------------------------------------------ symmetric heap */
 /*

@@ -61,6 +61,24 @@ def test_gated_grouped_gemm_and_ffn(capi, orc, T, H, F, E, k):
         assert orc.rel_fro(out.float().cpu(), want_out) <= TOL
 
 
+def test_ffn_with_banded_tile_walk(capi, orc):
+    """Experts with more row tiles than a band holds (the band shrunk to three row tiles; bands of
+    3, 3 and a rest): the tile order changes, the result does not."""
+    T, H, F, E, k = 2048, 256, 256, 4, 2
+    c = _case(orc, T, H, F, E, k, zipf=1.1)
+    assert int((c["offs"][1:] - c["offs"][:-1]).max()) // 128 > 3
+    want_y = orc.moe_ffn_ref(c["xq"], c["xs"], c["w13q"], c["w13s"], c["w2q"], c["w2s"], c["offs"])[0]
+    d = {n: c[n].cuda() for n in ("xq", "xs", "w13q", "w13s", "w2q", "w2s", "offs")}
+    capi.check(capi.lib().dk_set_walk_band_bytes(3 * 128 * H))
+    try:
+        y = capi.moe_ffn_fp8(d["xq"], d["xs"], d["w13q"], d["w13s"], d["w2q"], d["w2s"], d["offs"])
+        torch.cuda.synchronize()
+    finally:
+        capi.check(capi.lib().dk_set_walk_band_bytes(32 << 20))
+    assert capi.device_status()[0] == 0
+    assert orc.rel_fro(y.float().cpu(), want_y) <= TOL
+
+
 def test_grouped_gemm_empty_experts_and_errors(capi, orc):
     T, H, F, E, k = 128, 256, 128, 8, 1
     c = _case(orc, T, H, F, E, k)
