@@ -220,6 +220,12 @@ __global__ void __launch_bounds__(PERM_CHUNK) moe_place_kernel(const int* __rest
 // block), and also written as an e8m0 byte (log2(s) + 127) and into the scale atoms the
 // block-scaled tensor-core path reads: per 128 rows and four column blocks one 512-byte atom whose
 // byte r*4 + g (r = row slot 0..127, g = 0..3) is the byte of column block 4j + g.
+__device__ __forceinline__ float div_by_fma(float x, float d, float inv_d) {
+    const float q0 = x * inv_d;
+    const float r = fmaf(-q0, d, x);
+    return fmaf(r, inv_d, q0);
+}
+
 template <bool POW2>
 __global__ void __launch_bounds__(256, 4) quant_block128_kernel(const __nv_bfloat16* __restrict__ x, int R, int C,
                                                              const int* __restrict__ map, int map_mode,
@@ -293,7 +299,12 @@ __global__ void __launch_bounds__(256, 4) quant_block128_kernel(const __nv_bfloa
         if (threadIdx.x == 0 && e8 != nullptr) e8[blk] = static_cast<uint8_t>(b8);
     }
     if (threadIdx.x == 0 && s != nullptr) s[blk] = scale;
-    const float inv = 1.0f / scale;  // exact for a power of two
+    const float inv = 1.0f / scale;  // correctly rounded; exact for a power of two
+    // The CPU definition divides (x / scale, correctly rounded). The same bits come from q0 = x * inv,
+    // r = x - q0 * scale (exact in an FMA), q = q0 + r * inv whenever r does not underflow; with the scale
+    // in this range it can underflow only for quotients below 1e-7, which round to zero in e4m3
+    // either way (the smallest rounding boundary is 2^-10). A third of the instructions of a division.
+    const bool fast_div = scale >= 0x1p-80f && scale <= 0x1p80f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int r = br * 128 + r0 + 16 * i;
@@ -305,6 +316,8 @@ __global__ void __launch_bounds__(256, 4) quant_block128_kernel(const __nv_bfloa
             float2 y;
             if (POW2) {
                 y = make_float2(f.x * inv, f.y * inv);
+            } else if (fast_div) {
+                y = make_float2(div_by_fma(f.x, scale, inv), div_by_fma(f.y, scale, inv));
             } else {
                 y = make_float2(f.x / scale, f.y / scale);  // IEEE division: same bits as the CPU definition
             }

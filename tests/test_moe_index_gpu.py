@@ -84,8 +84,13 @@ def test_quant_bit_exact_and_golden(capi, orc):
     q, s = capi.quant_block128(x.cuda())
     assert np.array_equal(q.cpu().numpy(), fx["q"]) and np.array_equal(s.cpu().numpy(), fx["s"])
     g = torch.Generator().manual_seed(0)
-    for scale in (1.0, 1e-3, 300.0):
-        x = (torch.randn(512, 384, generator=g) * scale).to(torch.bfloat16)
+    # 1e-30 and 1e30 put the block scales outside the range in which the kernel replaces the division
+    # by its FMA form; the heavy-tailed case spreads the quotients over the whole e4m3 range
+    for scale in (1.0, 1e-3, 300.0, 1e-30, 1e30, "heavy"):
+        if scale == "heavy":
+            x = (torch.randn(4096, 512, generator=g) * torch.exp(3.0 * torch.randn(4096, 512, generator=g))).to(torch.bfloat16)
+        else:
+            x = (torch.randn(512, 384, generator=g) * scale).to(torch.bfloat16)
         x[5, 7] = 0.0
         q, s = capi.quant_block128(x.cuda())
         rq, rs = orc.quant_block128(x)
