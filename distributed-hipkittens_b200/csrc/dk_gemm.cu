@@ -40,7 +40,7 @@
 // All-gather mode (column-parallel GEMM, the projection BEFORE the row-parallel one): the rows of A
 // are sharded over the ranks (A_r [M/P, K]), every rank needs all of them against its own columns of
 // the weight. The six warps that have nothing to do in a plain GEMM push this rank's shard into the
-// peers' staging copies of A, 16 rows at a time with 16-byte peer stores, and count each piece into a
+// peers' staging copies of A, two rows at a time with 16-byte peer stores, and count each piece into a
 // per-(source, 128-row tile) counter at the destination with a release add. The TMA producer starts
 // with the tiles of its own rows (read from the caller's A), then walks the other shards in the
 // order rank+1, rank+2, ...; before the first load of a tile whose rows come from a peer it waits
@@ -50,6 +50,7 @@
 #include "dk_host.h"
 #include "dk_ptx.cuh"
 
+#include <algorithm>
 #include <cstdlib>
 
 namespace dk {
@@ -115,7 +116,11 @@ struct GemmArgs {
     unsigned ag_target;                  // value a counter has reached when its tile is complete
 };
 
-constexpr int AG_ROWS = 16;                  // rows per pushed piece
+// Rows per pushed piece. Small pieces matter twice: every pusher warp of the grid gets work (a warp
+// keeps 2 KB in flight, so the aggregate rate needs all of them to fill NVLink), and because the
+// pieces are dealt in the order nearest consumer first, the shard the next rank needs first arrives
+// first at full bandwidth instead of all shards arriving together at the end.
+constexpr int AG_ROWS = 2;
 constexpr int AG_PIECES = BM / AG_ROWS;      // pieces per 128-row tile
 
 enum : unsigned {
@@ -547,8 +552,8 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
     }
 
     // -------------------------------------------------------- all-gather pushers (warps 6..11)
-    // Every piece is 16 rows of this rank's shard = 16 * K contiguous bf16 at the source and at the
-    // destination. Pieces are dealt round-robin to the pusher warps of the whole grid, nearest
+    // Every piece is AG_ROWS rows of this rank's shard = AG_ROWS * K contiguous bf16 at the source and
+    // at the destination. Pieces are dealt round-robin to the pusher warps of the whole grid, nearest
     // consumer first: rank d works through the shards d, d+1, ..., so the shard of rank s is needed
     // first by s-1, then s-2, ...
     if (warp >= 6 && g.ag_world > 1 && g.ag_push) {
@@ -567,12 +572,12 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
             const uint4* src = g.ag_src + row0 * (g.K / 8);
             uint4* dst = g.ag_dst[d] + (static_cast<size_t>(g.ag_rank) * g.ag_shard_rows + row0) * (g.K / 8);
             int i = lane;
-            for (; i + 96 < nvec; i += 128) {
-                const uint4 v0 = src[i], v1 = src[i + 32], v2 = src[i + 64], v3 = src[i + 96];
-                dst[i] = v0;
-                dst[i + 32] = v1;
-                dst[i + 64] = v2;
-                dst[i + 96] = v3;
+            for (; i + 224 < nvec; i += 256) {  // eight 16-byte loads per lane in flight
+                uint4 v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = src[i + 32 * j];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) dst[i + 32 * j] = v[j];
             }
             for (; i < nvec; i += 32) dst[i] = src[i];
             // the lanes' stores are ordered before lane 0's release by the warp barrier; the release
@@ -900,7 +905,9 @@ int ag_gemm_impl(const void* A, const void* Bt, void* C, int M, int N, int K, vo
     g.N = N;
     g.K = K;
     g.tiles_m = M / BM / pair;
-    g.group_m = group_m_setting() / pair;
+    // raster groups never span two shards: all tiles of the rows already here come before the first
+    // tile that has to wait for a peer
+    g.group_m = std::min(group_m_setting() / pair, shard / BM / pair);
     if (g.group_m < 1) g.group_m = 1;
     g.tiles_n = (N + BN - 1) / BN;
     g.num_kb = (K + BK - 1) / BK;
