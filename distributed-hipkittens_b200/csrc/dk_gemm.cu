@@ -33,9 +33,10 @@
 // a release store of the call number into that tile's flag [rank] at the owner. Tiles are visited
 // with the owners rotating fastest (rank+1, rank+2, ..., this rank), see tile_coords: every link is
 // busy all the time and the partials of a tile arrive at its owner at about the same time.
-//   warps 6-11  reducers: for every tile of this rank's own rows that this CTA computes, wait
-//               (bounded) for the `world` flags, sum the `world` bf16 partials in fp32 in rank order
-//               and write bf16, while the MMA warp is already working on the next tile.
+//   warps 6-11  reducers: the tiles of this rank's own rows are dealt, a quarter tile at a time and in
+//               the order in which they are computed, over the reducer warps of the whole grid; for
+//               each the warps wait (bounded) for the `world` flags, sum the `world` bf16 partials in
+//               fp32 in rank order and write bf16, while the MMA warps are working on later tiles.
 //
 // All-gather mode (column-parallel GEMM, the projection BEFORE the row-parallel one): the rows of A
 // are sharded over the ranks (A_r [M/P, K]), every rank needs all of them against its own columns of
@@ -92,7 +93,7 @@ struct GemmArgs {
     int world, rank;
     int rows_per_rank;  // rows of the output owned by one rank (M when world == 1)
     int tiles_per_owner;  // reduce-scatter: row-tiles (of 128 * PAIR rows) per owner; 0 = one rank
-    int m_tile_rot;       // phased order only: first row-tile visited
+    int m_tile_rot;       // all-gather mode: first row-tile visited
     int group_m;          // row-tiles per raster group (reduce-scatter: per owner)
     int epi_mode;       // 0 direct stores, 1 TMA stores
     int phases;         // bit 0: GEMM tiles, bit 1: reduce this rank's rows
@@ -166,8 +167,7 @@ __device__ __forceinline__ void tile_coords(int t, const GemmArgs& g, int& m, in
     const int r = t - grp * per_group;
     m = first_m + r % gsz;
     n = r / gsz;
-    // phased reduce-scatter order (DK_GEMM_RS_ORDER=phased): all tiles of owner rank+1 first,
-    // ..., this rank's own rows last
+    // all-gather mode starts with the rows that are already here
     m += g.m_tile_rot;
     if (m >= g.tiles_m) m -= g.tiles_m;
 }
@@ -198,13 +198,13 @@ __device__ __forceinline__ bool epi_signal(const GemmArgs& g, const WaitCtx& wc,
 template <int UNR, int W>
 __device__ __forceinline__ void reduce_tile(const __nv_bfloat16* __restrict__ src,
                                             __nv_bfloat16* __restrict__ dst, int N, int world, int rt,
-                                            int tm, int n, int rtile, size_t slot_elems) {
-    constexpr int TILE_VECS = BM * (BN / 8);
+                                            int tm, int n, int rtile, size_t slot_elems, int vec_lo,
+                                            int vec_hi) {
     const uint4* tsrc = reinterpret_cast<const uint4*>(src + static_cast<size_t>(rtile) * (BM * BN));
     __nv_bfloat16* tdst = dst + static_cast<size_t>(tm) * BM * N + n * BN;
     const size_t slot_vecs = slot_elems / 8;
 #pragma unroll 1
-    for (int base = rt; base < TILE_VECS; base += RED_THREADS * UNR) {
+    for (int base = vec_lo + rt; base < vec_hi; base += RED_THREADS * UNR) {
         uint4 v[UNR][W];
         int off[UNR];
 #pragma unroll
@@ -215,7 +215,7 @@ __device__ __forceinline__ void reduce_tile(const __nv_bfloat16* __restrict__ sr
             const int j = (vi & 7) ^ (row_in & 7);
             const int row = (blk >> 2) * 32 + row_in;
             const int col = (blk & 3) * 64 + j * 8;
-            off[u] = (vi < TILE_VECS && n * BN + col + 8 <= N) ? row * N + col : -1;
+            off[u] = (vi < vec_hi && n * BN + col + 8 <= N) ? row * N + col : -1;
 #pragma unroll
             for (int s = 0; s < W; ++s)
                 if (s < world && off[u] >= 0)
@@ -588,18 +588,22 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
     }
 
     // -------------------------------------------------------- reducers (warps 6..11, world > 1)
-    // They walk the same tile list as the GEMM roles and pick the tiles whose rows this rank owns:
-    // the CTA that computes this rank's own partial of a tile (the last contribution to arrive,
-    // by the visiting order) also sums that tile, while the MMA warp is already on the next one.
+    // The tiles whose rows this rank owns are summed by the reducer warps of the WHOLE grid, a
+    // quarter of a 128-row tile (32 rows = four 4 KiB blocks of the staged image) per work item, items
+    // dealt round-robin over the CTAs in the order in which the tiles are computed. A tile is summed
+    // as soon as its `world` partials are there, by four CTAs at once, while the MMA warps are on later
+    // tiles; after the last wave every CTA has at most one quarter tile left instead of a few CTAs
+    // having a whole one.
     if (warp >= 6 && (g.phases & 2) != 0 && g.world > 1) {
         const int rt = threadIdx.x - (GEMM_THREADS - RED_THREADS);
         const size_t slot_elems = static_cast<size_t>(g.rows_per_rank) * g.tiles_n * BN;
+        constexpr int QUARTER_VECS = 32 * (BN / 8);
+        const int own_tiles = num_tiles / g.world;  // tile units (pairs) whose rows this rank owns
+        const int items = own_tiles * PAIR * 4;
         long long dbg_flag = 0, dbg_work = 0;
-        for (int t = unit; t < num_tiles; t += nunits) {
-            int m, n;
-            tile_coords(t, g, m, n);
-            m = m * PAIR + crank;
-            if ((m * BM) / g.rows_per_rank != g.rank) continue;
+        bool ok = true;
+        // one work item: quarter `quarter` of the 128-row tile m (a row-tile index of the whole output)
+        auto reduce_item = [&](int m, int n, int quarter) {
             long long c0 = clock64();
             const int tm = (m * BM - g.rank * g.rows_per_rank) / BM;
             const int rtile = tm * g.tiles_n + n;
@@ -607,12 +611,26 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs g) {
                 signal_wait_ge(g.red_flags + static_cast<size_t>(rtile) * g.world + rt, g.epoch, wc,
                                SITE_RS_FLAG, rtile);
             named_bar_sync(2, RED_THREADS);
-            if (*abort_sm) break;
+            if (*abort_sm) {
+                ok = false;
+                return;
+            }
             dbg_flag += clock64() - c0;
             c0 = clock64();
-            // 128 rows x 32 16-byte vectors; world * UNR = 16 vectors per thread in flight
-            reduce_tile<16 / W, W>(g.red_src, g.red_out, g.N, g.world, rt, tm, n, rtile, slot_elems);
+            // world * UNR = 16 vectors per thread in flight
+            reduce_tile<16 / W, W>(g.red_src, g.red_out, g.N, g.world, rt, tm, n, rtile, slot_elems,
+                                   quarter * QUARTER_VECS, (quarter + 1) * QUARTER_VECS);
             dbg_work += clock64() - c0;
+        };
+        // the owners take turns in the visiting order, this rank last of each round, so the i-th own
+        // tile is tile i * world + world - 1
+        for (int j = blockIdx.x; j < items && ok; j += gridDim.x) {
+            const int i = j / (4 * PAIR);
+            int m, n;
+            tile_coords(i * g.world + g.world - 1, g, m, n);
+            m = m * PAIR + (j >> 2) % PAIR;
+            if ((m * BM) / g.rows_per_rank != g.rank) continue;  // cannot happen in this order
+            reduce_item(m, n, j & 3);
         }
         if (g.dbg != nullptr && rt == 0) {
             g.dbg[blockIdx.x * DBG_SLOTS + DBG_RED_WAIT_FLAG] = dbg_flag;
@@ -811,18 +829,16 @@ int gemm_rs_impl(const void* A, const void* Bt, void* out, int M, int N, int Klo
     g.N = N;
     g.K = Kloc;
     g.tiles_m = M / BM / pair;   // tiles of 128 * pair rows
-    const char* order = std::getenv("DK_GEMM_RS_ORDER");
-    const bool phased = order != nullptr && std::string(order) == "phased";
-    // interleaved: world * group_m row-tiles are live at a time; keep that near the one-rank group
-    g.group_m = phased ? group_m_setting() / pair : group_m_setting() / pair / world;
+    // world * group_m row-tiles are live at a time; keep that near the one-rank group
+    g.group_m = group_m_setting() / pair / world;
     if (g.group_m < 1) g.group_m = 1;
     g.tiles_n = (N + BN - 1) / BN;
     g.num_kb = (Kloc + BK - 1) / BK;
     g.world = world;
     g.rank = rank;
     g.rows_per_rank = mloc;
-    g.tiles_per_owner = phased ? 0 : mloc / BM / pair;
-    g.m_tile_rot = phased ? ((rank + 1) % world) * (mloc / BM / pair) : 0;
+    g.tiles_per_owner = mloc / BM / pair;
+    g.m_tile_rot = 0;
     // Pushes to peers always use TMA bulk stores: with direct 16-byte stores to peer memory an
     // 8-GPU run stalled until its peer waits ran out, so that variant is not offered across GPUs.
     (void)epilogue;
