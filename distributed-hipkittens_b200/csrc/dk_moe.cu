@@ -18,6 +18,8 @@
 #include <mutex>
 #include <string>
 
+#include <algorithm>
+
 #include "dk_moe_int.h"
 
 namespace dk {
@@ -209,7 +211,7 @@ __global__ void __launch_bounds__(PERM_CHUNK) moe_place_kernel(const int* __rest
 }
 
 // ------------------------------------------------------------------------------------ quantise
-// One CTA per 128x128 block. 256 threads; thread t owns column chunk (t % 16) * 8 of rows
+// One 128x128 block at a time per CTA (grid-stride over the blocks that exist). 256 threads; thread t owns column chunk (t % 16) * 8 of rows
 // t/16 + 16*i, i = 0..7. Source rows come straight from x, or through a row map:
 //   map_mode 0: row r of x;  1: row map[r] / k of x (gather), zeros where map[r] < 0;
 //   2: row r of x where map[r] >= 0, zeros elsewhere (rows already in place, padding undefined)
@@ -235,11 +237,18 @@ __global__ void __launch_bounds__(256, 4) quant_block128_kernel(const __nv_bfloa
                                                              const int* __restrict__ map2,
                                                              const int* __restrict__ row_limit, const EpWait wait) {
     __shared__ float red[8];
-    const int bc = blockIdx.x, br = blockIdx.y;
-    if (row_limit != nullptr && br * 128 >= *row_limit) return;
+    // The grid is sized for the GPU, not for R: with a row limit read on the device most of the R / 128
+    // row blocks may not exist, and a CTA per block would spend the kernel launching CTAs that exit.
+    const int cblocks = C / 128;
+    const int rows = row_limit != nullptr ? min(*row_limit, R) : R;
+    const int nblocks = (rows / 128) * cblocks;
+    if (static_cast<int>(blockIdx.x) >= nblocks) return;
     if (!ep_wait_sources(wait)) return;
     const int cchunk = (threadIdx.x & 15) * 8;
     const int r0 = threadIdx.x >> 4;
+    for (int blk_i = blockIdx.x; blk_i < nblocks; blk_i += gridDim.x) {
+    const int br = blk_i / cblocks, bc = blk_i - br * cblocks;
+    __syncthreads();  // the previous block's maxima have been read
     // The 8 x 8 values of this thread stay packed as bf16 (32 registers instead of 64): the kernel is
     // bound by how many row loads an SM keeps in flight, i.e. by how many CTAs fit.
     uint4 u[8];
@@ -328,6 +337,7 @@ __global__ void __launch_bounds__(256, 4) quant_block128_kernel(const __nv_bfloa
         }
         *reinterpret_cast<uint2*>(q + static_cast<size_t>(r) * C + bc * 128 + cchunk) = make_uint2(w[0], w[1]);
     }
+    }  // blocks of this CTA
 }
 
 // ------------------------------------------------------------------------------------ combine
@@ -434,7 +444,11 @@ int quant_block128_launch(const void* x, int R, int C, const int* map, int map_m
     if (R == 0) return DK_OK;
     DK_REQUIRE(x && q, "null buffer");
     DK_REQUIRE(!pow2 || (reinterpret_cast<uintptr_t>(atoms) & 15) == 0, "the scale atoms must be 16-byte aligned");
-    const dim3 grid(C / 128, R / 128);
+    int sms = 0;
+    const int src = sm_count(&sms);
+    if (src != DK_OK) return src;
+    const long long all = static_cast<long long>(C / 128) * (R / 128);
+    const int grid = static_cast<int>(std::min<long long>(all, 4ll * sms * 2));  // two rounds of resident CTAs at most
     if (pow2)
         quant_block128_kernel<true><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), R, C, map, map_mode, k,
                                                           static_cast<uint8_t*>(q), s, static_cast<uint8_t*>(e8),

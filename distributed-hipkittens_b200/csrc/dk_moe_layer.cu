@@ -25,6 +25,8 @@
 //                    the block-scaled tensor-core path reads (they are per row by construction).
 //   partial[d]       [T_loc, H] bf16 on the home rank: sum over the token's experts on rank d of
 //                    w * y, formed in fp32 on rank d; the home rank adds the partials in rank order
+#include <algorithm>
+
 #include <cuda_fp8.h>
 
 #include "dk_moe_int.h"
@@ -282,11 +284,13 @@ struct EpGatherQArgs {
     EpWait wait;
 };
 __global__ void __launch_bounds__(256) ep_gather_q_kernel(const EpGatherQArgs a) {
-    const int row0 = blockIdx.x * 8;
-    if (row0 >= *a.row_limit) return;
+    const int rows = min(*a.row_limit, a.cap);
+    if (static_cast<int>(blockIdx.x) * 8 >= rows) return;
     if (!ep_wait_sources(a.wait)) return;
-    const int r = row0 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (r >= a.cap) return;
+    const int lane = threadIdx.x & 31;
+    // grid-stride over the rows that exist (a CTA per eight rows of the capacity would mostly launch
+    // CTAs that exit)
+    for (int r = blockIdx.x * 8 + (threadIdx.x >> 5); r < rows; r += gridDim.x * 8) {
     const int pair = a.por[r];
     const int src = pair >= 0 ? a.slot[pair / a.k] : -1;
     const int nvec = a.H / 16;
@@ -307,6 +311,7 @@ __global__ void __launch_bounds__(256) ep_gather_q_kernel(const EpGatherQArgs a)
     const uint32_t* sc = reinterpret_cast<const uint32_t*>(a.toks + static_cast<size_t>(src < 0 ? 0 : src) * a.sb);
     for (int j = lane; j < nj; j += 32)
         *reinterpret_cast<uint32_t*>(atom_row + static_cast<size_t>(j) * 512) = src >= 0 ? __ldcg(sc + j) : 0x7f7f7f7fu;
+    }  // rows of this warp
 }
 
 // ---- expert-side combine: for every token that arrived here, the weighted sum of the outputs of its
@@ -599,7 +604,7 @@ int dk_moe_ep_layer(const dk_moe_ep_args* a, const dk_view* view, unsigned epoch
             g.sb = sb;
             g.k = k;
             g.wait = w;
-            ep_gather_q_kernel<<<(cap + 7) / 8, 256, 0, st>>>(g);
+            ep_gather_q_kernel<<<std::min((cap + 7) / 8, 16 * sms), 256, 0, st>>>(g);
             DK_CUDA_OK(cudaGetLastError());
         } else {
             rc = quant_block128_launch(world > 1 ? at(L.tokbuf) : a->x, cap, H, por + static_cast<size_t>(rank) * cap,
