@@ -327,49 +327,68 @@ struct EpCombineArgs {
     int T_loc, k, hvec, epr, rank;
     EpSignal sig;
 };
+// One warp per token (eight tokens per CTA at a time, no CTA-wide barrier per token): lanes < k fetch
+// the token's pairs, the warp shares them by shuffle, then every lane sums its 16-byte columns with
+// the rows of two column steps requested before the first is used.
 __global__ void __launch_bounds__(256) ep_combine_push_kernel(const EpCombineArgs a) {
-    __shared__ int row_s[8];
-    __shared__ float w_s[8];
     const int n = *a.ntok;
-    for (int s = blockIdx.x; s < n; s += gridDim.x) {
+    const int lane = threadIdx.x & 31;
+    const int nwarps = gridDim.x * (blockDim.x >> 5);
+    for (int s = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); s < n; s += nwarps) {
         const int t = a.tok_of_slot[s];
-        __syncthreads();
-        if (threadIdx.x < a.k) {
-            const size_t at = static_cast<size_t>(t) * a.k + threadIdx.x;
+        int my_row = -1;
+        float my_w = 0.f;
+        if (lane < a.k) {
+            const size_t at = static_cast<size_t>(t) * a.k + lane;
             const int e = a.all_idx[at];
             const bool here = e >= 0 && e / a.epr == a.rank;
-            row_s[threadIdx.x] = here ? a.rop[at] : -1;   // -1 also for a pair the permutation left out
-            w_s[threadIdx.x] = a.all_w[at];
+            my_row = here ? a.rop[at] : -1;   // -1 also for a pair the permutation left out
+            my_w = a.all_w[at];
         }
-        __syncthreads();
+        int row[8];
+        float wt[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            row[j] = __shfl_sync(0xffffffffu, my_row, j);
+            wt[j] = __shfl_sync(0xffffffffu, my_w, j);
+        }
         const int home = t / a.T_loc;
         uint4* dst = a.partial[home] + static_cast<size_t>(t - home * a.T_loc) * a.hvec;
-        for (int c = threadIdx.x; c < a.hvec; c += blockDim.x) {
-            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            uint4 v[8];
-            // all of the token's rows on this rank are requested before the first one is used
+        for (int c0 = lane; c0 < a.hvec; c0 += 64) {
+            uint4 v[2][8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-                v[j] = (j < a.k && row_s[j] >= 0) ? a.y[static_cast<size_t>(row_s[j]) * a.hvec + c] : make_uint4(0, 0, 0, 0);
+            for (int u = 0; u < 2; ++u) {
+                const int c = c0 + 32 * u;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                if (j < a.k && row_s[j] >= 0) {
-                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[j]);
-                    const float wj = w_s[j];
+                for (int j = 0; j < 8; ++j)
+                    v[u][j] = (c < a.hvec && row[j] >= 0) ? a.y[static_cast<size_t>(row[j]) * a.hvec + c]
+                                                          : make_uint4(0, 0, 0, 0);
+            }
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float2 f = __bfloat1622float2(h[i]);
-                        acc[2 * i] += wj * f.x;
-                        acc[2 * i + 1] += wj * f.y;
+            for (int u = 0; u < 2; ++u) {
+                const int c = c0 + 32 * u;
+                if (c >= a.hvec) break;
+                float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (row[j] >= 0) {
+                        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[u][j]);
+                        const float wj = wt[j];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float2 f = __bfloat1622float2(h[i]);
+                            acc[2 * i] += wj * f.x;
+                            acc[2 * i + 1] += wj * f.y;
+                        }
                     }
                 }
+                uint4 o;
+                o.x = pack_bf16x2(acc[0], acc[1]);
+                o.y = pack_bf16x2(acc[2], acc[3]);
+                o.z = pack_bf16x2(acc[4], acc[5]);
+                o.w = pack_bf16x2(acc[6], acc[7]);
+                dst[c] = o;
             }
-            uint4 o;
-            o.x = pack_bf16x2(acc[0], acc[1]);
-            o.y = pack_bf16x2(acc[2], acc[3]);
-            o.z = pack_bf16x2(acc[4], acc[5]);
-            o.w = pack_bf16x2(acc[6], acc[7]);
-            dst[c] = o;
         }
     }
     ep_signal_done(a.sig);
@@ -384,35 +403,50 @@ struct EpFinalArgs {
     EpWait wait;
 };
 __global__ void __launch_bounds__(256) ep_final_kernel(const EpFinalArgs a) {
-    __shared__ int has_s[DK_MAX_RANKS];
     if (!ep_wait_sources(a.wait)) return;
-    for (int tl = blockIdx.x; tl < a.T_loc; tl += gridDim.x) {
+    const int lane = threadIdx.x & 31;
+    const int nwarps = gridDim.x * (blockDim.x >> 5);
+    // one warp per token
+    for (int tl = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); tl < a.T_loc; tl += nwarps) {
         const int t = a.rank * a.T_loc + tl;
-        __syncthreads();
-        if (threadIdx.x < a.world) has_s[threadIdx.x] = a.slot[static_cast<size_t>(threadIdx.x) * a.T + t] >= 0;
-        __syncthreads();
-        for (int c = threadIdx.x; c < a.hvec; c += blockDim.x) {
-            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        const bool mine = lane < a.world && a.slot[static_cast<size_t>(lane) * a.T + t] >= 0;
+        const unsigned has = __ballot_sync(0xffffffffu, mine);  // ranks the token was sent to
+        for (int c0 = lane; c0 < a.hvec; c0 += 64) {
+            uint4 v[2][DK_MAX_RANKS];
 #pragma unroll
-            for (int d = 0; d < DK_MAX_RANKS; ++d) {
-                if (d < a.world && has_s[d]) {
+            for (int u = 0; u < 2; ++u) {
+                const int c = c0 + 32 * u;
+#pragma unroll
+                for (int d = 0; d < DK_MAX_RANKS; ++d)
                     // written by rank d during this call: read past L1
-                    const uint4 u = __ldcg(a.partial + (static_cast<size_t>(d) * a.T_loc + tl) * a.hvec + c);
-                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+                    v[u][d] = (c < a.hvec && ((has >> d) & 1u))
+                                  ? __ldcg(a.partial + (static_cast<size_t>(d) * a.T_loc + tl) * a.hvec + c)
+                                  : make_uint4(0, 0, 0, 0);
+            }
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float2 f = __bfloat1622float2(h[i]);
-                        acc[2 * i] += f.x;
-                        acc[2 * i + 1] += f.y;
+            for (int u = 0; u < 2; ++u) {
+                const int c = c0 + 32 * u;
+                if (c >= a.hvec) break;
+                float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+                for (int d = 0; d < DK_MAX_RANKS; ++d) {
+                    if ((has >> d) & 1u) {
+                        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[u][d]);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float2 f = __bfloat1622float2(h[i]);
+                            acc[2 * i] += f.x;
+                            acc[2 * i + 1] += f.y;
+                        }
                     }
                 }
+                uint4 o;
+                o.x = pack_bf16x2(acc[0], acc[1]);
+                o.y = pack_bf16x2(acc[2], acc[3]);
+                o.z = pack_bf16x2(acc[4], acc[5]);
+                o.w = pack_bf16x2(acc[6], acc[7]);
+                a.out[static_cast<size_t>(tl) * a.hvec + c] = o;
             }
-            uint4 o;
-            o.x = pack_bf16x2(acc[0], acc[1]);
-            o.y = pack_bf16x2(acc[2], acc[3]);
-            o.z = pack_bf16x2(acc[4], acc[5]);
-            o.w = pack_bf16x2(acc[6], acc[7]);
-            a.out[static_cast<size_t>(tl) * a.hvec + c] = o;
         }
     }
 }
@@ -661,7 +695,7 @@ int dk_moe_ep_layer(const dk_moe_ep_args* a, const dk_view* view, unsigned epoch
         f.rank = rank;
         rc = make_wait(view, EP_PH_COMBINE, epoch, &f.wait);
         if (rc != DK_OK) return rc;
-        const int grid = a->T_loc < 4 * sms ? a->T_loc : 4 * sms;
+        const int grid = std::min((a->T_loc + 7) / 8, 4 * sms);  // a warp per token
         ep_final_kernel<<<grid, 256, 0, st>>>(f);
         DK_CUDA_OK(cudaGetLastError());
         if (world > 1 && epoch == DK_EPOCH_DEVICE) {
