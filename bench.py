@@ -640,7 +640,8 @@ class Moe:
         self.scale = 1e12
         # route, memset, hist, scan, place, 2 slot kernels, (dispatch), quantise, 2 grouped GEMMs,
         # combine push, final sum
-        self.launches_per_step = 12 if P == 1 else 13
+        # (one rank without the fp8 dispatch: no dispatch kernel, the quantiser gathers straight from x)
+        self.launches_per_step = 12 if (P == 1 and self.mode != 2) else 13
         self.gemm_ms = None
         ctx.barrier()
 
