@@ -30,7 +30,9 @@ def pair_mode(capi, request):
 
 @pytest.mark.parametrize("pair_mode", [1, 0], indirect=True)
 @pytest.mark.parametrize("world,M,N,K", [(2, 512, 512, 256), (4, 1024, 768, 512), (8, 2048, 264, 1024),
-                                         (2, 256, 512, 128), (4, 2048, 1024, 256)])
+                                         (2, 256, 512, 128), (4, 2048, 1024, 256),
+                                         # more quarter-tile reduction items than CTAs (512 per rank), as at full size
+                                         (8, 8192, 4096, 128)])
 def test_gemm_rs_all_ranks_on_one_gpu(capi, orc, world, M, N, K, pair_mode):
     epilogue = -1
     buf, views, ws = _fake_job(capi, world, M, N)
