@@ -292,3 +292,57 @@ def test_pow2_block_quantiser(orc):
     s_rows = e[:, :, None].expand(-1, -1, 4).reshape(2, 12).repeat_interleave(128, dim=0)   # [R, C/32]
     assert torch.allclose(orc.mx_dequant(q, s_rows), d)
     assert torch.equal(orc.mx_sf_atoms(s_rows), atoms)
+
+
+def test_rows128_quantiser_of_the_fp8_dispatch(orc):
+    """1x128 power-of-two row scales: a row's bytes and scales depend on that row alone (so tokens
+    can be quantised where they live, before they are permuted into expert order); where all rows of
+    a 128-row block are equal they are the 128x128 quantiser's; the atom layout puts row slot
+    i = 32*i1 + i0 at bytes i0*16 + i1*4 .. +3 of each atom."""
+    g = torch.Generator().manual_seed(12)
+    x = (torch.randn(256, 640, generator=g) * torch.logspace(-2, 2, 256)[:, None]).to(torch.bfloat16)
+    x[7] = 0
+    q, s, e = orc.quant_rows128_pow2(x)
+    assert q.shape == (256, 640) and s.shape == (256, 5) and e.shape == (256, 5)
+    assert bool((s[7] == 1.0).all()) and bool((e[7] == 127).all()) and bool((q[7] == 0).all())
+    perm = torch.randperm(256, generator=g)
+    qp, sp, ep = orc.quant_rows128_pow2(x[perm])
+    assert torch.equal(qp, q[perm]) and torch.equal(ep, e[perm])
+    one = orc.quant_rows128_pow2(x[33:34])
+    assert torch.equal(one[0][0], q[33]) and torch.equal(one[2][0], e[33])
+    qf = q.view(torch.float8_e4m3fn).float().reshape(256, 5, 128)
+    gmax = qf.abs().amax(dim=2)
+    live = x.float().reshape(256, 5, 128).abs().amax(dim=2) > 0
+    assert bool((gmax[live] > 223.0).all()) and float(gmax.max()) <= 448.0     # group maximum in (224, 448]
+    assert orc.rel_fro(orc.dequant_rows128(q, s), x.float()) <= 0.04
+    # a block of equal rows: the row scales are the block's scales
+    xb = x[40:41].expand(128, -1).contiguous()
+    qb, sb, eb = orc.quant_block128_pow2(xb)
+    qr, sr, er = orc.quant_rows128_pow2(xb)
+    assert torch.equal(qb, qr) and bool((er == eb[0][None, :]).all())
+    # atoms
+    atoms = orc.rows128_scales_to_block_atoms(e)
+    assert atoms.shape == (2, 2, 512)
+    for r, kb in ((0, 0), (37, 2), (255, 4), (130, 3)):
+        i = r % 128
+        assert int(atoms[r // 128, kb // 4, (i % 32) * 16 + (i // 32) * 4 + kb % 4]) == int(e[r, kb])
+    assert int(atoms[0, 1, 0 * 16 + 0 * 4 + 1]) == 127        # column block 5 does not exist: scale 1
+    # and the uniform form is the special case of equal rows
+    assert torch.equal(orc.rows128_scales_to_block_atoms(er), orc.block128_scales_to_block_atoms(eb).reshape(1, 2, 512))
+
+
+def test_ffn_with_row_scales_reduces_to_block_scales(orc):
+    """moe_ffn_rows_pow2_ref with row scales that are constant inside every 128-row block is
+    moe_ffn_pow2_ref."""
+    x, logits, w13q, w13s, w2q, w2s = orc.make_moe_inputs(256, 256, 128, 4, 2, seed=3)
+    idx, w = orc.moe_route(logits, 2)
+    rop, por, offs, counts = orc.moe_permute(idx, 4)
+    rows = orc.moe_gather_rows(x, por, 2)
+    xq, xs, _ = orc.quant_block128_pow2(rows)
+    p13 = [orc.quant_block128_pow2(orc.dequant_block128(w13q[e], w13s[e]).to(torch.bfloat16)) for e in range(4)]
+    p2 = [orc.quant_block128_pow2(orc.dequant_block128(w2q[e], w2s[e]).to(torch.bfloat16)) for e in range(4)]
+    st = lambda parts, i: torch.stack([p[i] for p in parts])
+    a = orc.moe_ffn_pow2_ref(xq, xs, st(p13, 0), st(p13, 1), st(p2, 0), st(p2, 1), offs)[0]
+    xs_rows = xs.repeat_interleave(128, dim=0)
+    b = orc.moe_ffn_rows_pow2_ref(xq, xs_rows, st(p13, 0), st(p13, 1), st(p2, 0), st(p2, 1), offs)[0]
+    assert torch.allclose(a, b, rtol=1e-6, atol=1e-6)
