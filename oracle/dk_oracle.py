@@ -16,6 +16,9 @@ What each function restates, by path inside the reference project:
                       kernels/cdna4/gemm/mxfp8/MXFP8_8wave/8_wave_NT.cu:286-327. Those use 1x32 e8m0
                       scales; here the blocks are 128x128 with fp32 scales.
   grouped / ffn       CPU-loop pattern of kernels/cdna4/gemm/fp8fp32/FP8_8wave/8_wave.cu:445-476
+  quant_rows128_pow2 / the same quantise-then-dequantise pattern for 1x128 row groups with power-of-two
+  moe_ffn_rows_pow2_ref  scales (what the expert-parallel layer sends between GPUs as fp8); no counterpart
+                      in the reference, which quantises nothing on the way between GPUs
 
 PARITY PINNING. The reference holds exactly one check on this path: the example's seeds,
 initialisation and threshold for the GEMM; `example_inputs` + `example_check` restate it and
