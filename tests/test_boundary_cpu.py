@@ -109,6 +109,21 @@ def test_argument_errors_need_no_gpu(capi):
     assert L.dk_allreduce(None, None, 8, -1, None, None) == capi.ERR_ARG
     assert L.dk_set_peer_wait_ms(0) == capi.ERR_ARG
     assert L.dk_set_peer_wait_ms(20000) == 0
+    assert L.dk_set_walk_band_bytes(0) == capi.ERR_ARG
+    assert L.dk_set_walk_band_bytes(32 << 20) == 0
+    assert L.dk_mx_pair_mode(2) == capi.ERR_ARG and L.dk_mx_pair_mode(-1) == 0
+    # the one-call MoE layer: shapes and scale modes are checked before anything is launched
+    assert capi.moe_ep_workspace_bytes(256, 2, 8, 256, 128, 1) > 0
+    assert capi.moe_ep_workspace_bytes(256, 2, 8, 200, 128, 1) == 0       # H not a multiple of 128
+    assert capi.moe_ep_workspace_bytes(256, 2, 9, 256, 128, 2) == 0       # E not a multiple of world
+    a = capi.DkMoeEpArgs()
+    a.T_loc, a.k, a.E, a.H, a.F, a.scale_mode = 256, 2, 8, 256, 128, 3
+    for f in ("x", "logits", "w13q", "w13s", "w2q", "w2s", "out", "workspace"):
+        setattr(a, f, 4096)
+    assert L.dk_moe_ep_layer(C.byref(a), None, 0, 15, None) == capi.ERR_ARG
+    assert b"scale_mode" in L.dk_last_error_string()
+    a.scale_mode = 2
+    assert L.dk_moe_ep_layer(C.byref(a), None, 0, 16, None) == capi.ERR_ARG      # phases outside 1..15
 
 
 # ---- host bootstrap between two processes (no GPU involved) -----------------------------------
