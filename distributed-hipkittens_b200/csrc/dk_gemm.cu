@@ -118,7 +118,7 @@ struct GemmArgs {
 };
 
 // Rows per pushed piece. Small pieces matter twice: every pusher warp of the grid gets work (a warp
-// keeps 2 KB in flight, so the aggregate rate needs all of them to fill NVLink), and because the
+// keeps 4 KB in flight, so the aggregate rate needs all of them to fill NVLink), and because the
 // pieces are dealt in the order nearest consumer first, the shard the next rank needs first arrives
 // first at full bandwidth instead of all shards arriving together at the end.
 constexpr int AG_ROWS = 2;
